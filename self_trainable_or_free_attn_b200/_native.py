@@ -1,0 +1,89 @@
+"""ctypes binding of libechosparse_sm100.so (the C ABI declared in include/echosparse_sm100.h).
+
+There is no fallback: if the library is missing or a call fails, this raises. PyTorch tensors are passed as raw device
+pointers; the launch goes on torch's current CUDA stream.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "_lib", "libechosparse_sm100.so")
+
+_P = ctypes.c_void_p
+_I = ctypes.c_int32
+_F = ctypes.c_float
+
+# name -> argument types (all return int unless listed in _RESTYPES)
+SIGNATURES = {
+    "es_last_error": [],
+    "es_abi_version": [],
+    "es_launch_count": [],
+    "es_device_status": [_P],
+    "es_block_attention": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F, _P],
+    "es_sparse_attention": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F,
+                            _P],
+    "es_exact_fallback": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _P],
+    "es_compensate_fallback": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "es_block_means": [_P, _P, _P, _P, _I, _I, _P],
+    "es_select_blocks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
+    "es_estimate_skipped": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "es_full_step_scales": [_P, _P, _P, _P, _I, _I, _P],
+    "es_pack_plan": [_P, _P, _I, _I, _I, _I, _P],
+    "es_rebuild_plan": [_P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _P],
+    "es_reps_gram_splits": [_I],
+    "es_reps_metric": [_P, _P, _P, _P, _P, _I, _I, _P],
+    "es_reps_kmeans": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+}
+_RESTYPES = {"es_last_error": ctypes.c_char_p, "es_launch_count": ctypes.c_longlong}
+
+_lib = None
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def load():
+    """Opens the shared library and declares every entry point. Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise NativeError(f"{LIB_PATH} is missing: build it with `python -m self_trainable_or_free_attn_b200.build` "
+                              f"(there is no CPU or Triton fallback)")
+        lib = ctypes.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = args
+            fn.restype = _RESTYPES.get(name, ctypes.c_int)
+        _lib = lib
+    return _lib
+
+
+def last_error():
+    return load().es_last_error().decode()
+
+
+def check(status, what):
+    if status != 0:
+        raise NativeError(f"{what} failed ({status}): {last_error()}")
+
+
+def device_status():
+    """Synchronises the current device and returns (and clears) the kernels' status word; 0 means fine."""
+    out = ctypes.c_int32(0)
+    check(load().es_device_status(ctypes.byref(out)), "es_device_status")
+    return out.value
+
+
+def launch_count():
+    return int(load().es_launch_count())
+
+
+def ptr(t):
+    """Device pointer of a tensor (None -> NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr():
+    import torch
+    return torch.cuda.current_stream().cuda_stream

@@ -1,0 +1,92 @@
+// Library-wide pieces of the C ABI: last-error text, device status word, launch counter, tensor-map encoder.
+#include "es_api_internal.h"
+
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+namespace es {
+
+static thread_local char g_error[512] = "";
+static std::atomic<long long> g_launches{0};
+
+// Written by a kernel whose bounded wait ran out (the code says which wait). One word per device, in that device's
+// copy of this module.
+__device__ int g_status_word = 0;
+
+int set_error(int code, const char* msg) {
+    std::snprintf(g_error, sizeof(g_error), "%s", msg ? msg : "");
+    return code;
+}
+
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+int* device_status_ptr() {
+    static int* ptrs[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_status_word) != cudaSuccess) return nullptr;
+        ptrs[dev] = static_cast<int*>(p);
+    }
+    return ptrs[dev];
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+int encode_tensor_map(CUtensorMap* m, CUtensorMapDataType dt, uint32_t rank, void* base, const cuuint64_t* dims,
+                      const cuuint64_t* strides_bytes, const cuuint32_t* box, const cuuint32_t* elem_strides,
+                      CUtensorMapSwizzle swizzle) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return set_error(-3, "cuTensorMapEncodeTiled is not available from this driver");
+    CUresult r = fn(m, dt, rank, base, dims, strides_bytes, box, elem_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        char buf[128];
+        std::snprintf(buf, sizeof(buf), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+        return set_error(-3, buf);
+    }
+    return 0;
+}
+
+}  // namespace es
+
+extern "C" const char* es_last_error(void) { return es::g_error; }
+
+extern "C" int es_abi_version(void) { return 1; }
+
+extern "C" long long es_launch_count(void) { return es::g_launches.load(std::memory_order_relaxed); }
+
+// Reads the status word of the current device and clears it. Synchronises the device.
+extern "C" int es_device_status(int32_t* status_out) {
+    int* p = es::device_status_ptr();
+    if (!p || !status_out) return es::set_error(-1, "es_device_status: no device or null pointer");
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return es::set_error(-2, cudaGetErrorString(e));
+    int v = 0;
+    e = cudaMemcpy(&v, p, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess) return es::set_error(-2, cudaGetErrorString(e));
+    *status_out = v;
+    if (v != 0) {
+        int zero = 0;
+        cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice);
+    }
+    return 0;
+}

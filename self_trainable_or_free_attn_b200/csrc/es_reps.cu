@@ -1,0 +1,396 @@
+// Four representatives per 64-token kv block, clustered in the query metric
+// (reference: echosparse/kernels/representatives.py:1-166).
+//
+//   G_h = Q_h^T Q_h / (D L) + 1e-3 mean(diag) I;  M_h = chol(G_h) (lower, pivots clamped), stored bf16
+//   64 probes per head: scaled means of evenly spaced 64-row query blocks, bf16
+//   per kv block: X = K M, token weights from the probes' softmaxes, weighted Lloyd from four 16-token groups,
+//   output = plain means of K and V over each final cluster (bf16) and log2 of the cluster sizes (-inf when empty).
+//
+// The Gram matrix is accumulated as per-split partial sums that the Cholesky kernel adds in a fixed order, so the
+// metric is reproducible bit for bit (the reference adds with atomics).
+#include "es_api_internal.h"
+
+#include <cuda_bf16.h>
+#include <math.h>
+
+namespace es {
+
+constexpr int HD = 128;
+constexpr int NP = 64;            // probes per head
+
+__device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// ------------------------------------------------------------------------------------------------ Gram partials
+// parts[h][split] = sum over the split's rows of q_r q_r^T. Thread (ty, tx) owns an 8 x 8 patch.
+__global__ void __launch_bounds__(256)
+gram_kernel(const __nv_bfloat16* __restrict__ q, float* __restrict__ parts, int L, int H, int rows_per_split,
+            int nsplit) {
+    __shared__ __align__(16) float rows[32][HD];
+    const int h = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x;
+    const int ty = tid >> 4, tx = tid & 15;
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+    const int r_begin = sp * rows_per_split, r_end = min(L, r_begin + rows_per_split);
+    for (int r0 = r_begin; r0 < r_end; r0 += 32) {
+        // 32 rows x 256 B: thread -> (row tid / 8, two 16-byte pieces)
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int rr = tid >> 3, c16 = (tid & 7) + 8 * x;
+            const int row = r0 + rr;
+            uint4 w = make_uint4(0, 0, 0, 0);
+            if (row < r_end) w = *reinterpret_cast<const uint4*>(q + ((size_t)row * H + h) * HD + c16 * 8);
+            float* d = &rows[rr][c16 * 8];
+            d[0] = bf_lo(w.x); d[1] = bf_hi(w.x); d[2] = bf_lo(w.y); d[3] = bf_hi(w.y);
+            d[4] = bf_lo(w.z); d[5] = bf_hi(w.z); d[6] = bf_lo(w.w); d[7] = bf_hi(w.w);
+        }
+        __syncthreads();
+#pragma unroll 4
+        for (int r = 0; r < 32; ++r) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&rows[r][8 * ty]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&rows[r][8 * ty + 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&rows[r][8 * tx]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&rows[r][8 * tx + 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    float* out = parts + ((size_t)h * nsplit + sp) * HD * HD;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        float4* o = reinterpret_cast<float4*>(out + (8 * ty + i) * HD + 8 * tx);
+        o[0] = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+        o[1] = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ metric
+// G = (sum of partials) * scale^2 / L, regularised, then right-looking Cholesky with clamped pivots
+// (representatives.py:49-63, 163-165). One CTA per head; the matrix lives in shared memory.
+__global__ void __launch_bounds__(256)
+metric_kernel(const float* __restrict__ parts, __nv_bfloat16* __restrict__ metric, float* __restrict__ gram_out,
+              int nsplit, float norm) {
+    extern __shared__ float sm[];
+    float* A = sm;                 // [128][129]
+    float* Lm = A + HD * 129;      // [128][129]
+    float* lj = Lm + HD * 129;     // [128]
+    __shared__ float red[8];
+    __shared__ float s_eps, s_diag;
+    const int h = blockIdx.x, tid = threadIdx.x;
+    for (int e = tid; e < HD * HD; e += 256) {
+        float s = 0.f;
+        for (int p = 0; p < nsplit; ++p) s += parts[((size_t)h * nsplit + p) * HD * HD + e];
+        A[(e >> 7) * 129 + (e & 127)] = s * norm;
+        Lm[(e >> 7) * 129 + (e & 127)] = 0.f;
+    }
+    __syncthreads();
+    float dg = tid < HD ? A[tid * 129 + tid] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, o);
+    if ((tid & 31) == 0) red[tid >> 5] = dg;
+    __syncthreads();
+    if (tid == 0) s_diag = (((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]))) / HD;
+    __syncthreads();
+    if (tid < HD) A[tid * 129 + tid] += 1e-3f * s_diag;
+    __syncthreads();
+    if (gram_out)
+        for (int e = tid; e < HD * HD; e += 256) gram_out[(size_t)h * HD * HD + e] = A[(e >> 7) * 129 + (e & 127)];
+    dg = tid < HD ? A[tid * 129 + tid] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, o);
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = dg;
+    __syncthreads();
+    if (tid == 0)
+        s_eps = (((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]))) / HD * 1e-12f;
+    __syncthreads();
+    for (int j = 0; j < HD; ++j) {
+        if (tid < HD) {
+            const float piv = fmaxf(A[j * 129 + j], s_eps);
+            const float v = tid >= j ? A[tid * 129 + j] / sqrtf(piv) : 0.f;
+            lj[tid] = v;
+            Lm[tid * 129 + j] = v;
+        }
+        __syncthreads();
+        // A -= lj lj^T on the trailing block (rows / columns before j have lj = 0)
+        for (int e = tid; e < HD * HD; e += 256) {
+            const int r = e >> 7, c = e & 127;
+            if (r >= j && c >= j) A[r * 129 + c] -= lj[r] * lj[c];
+        }
+        __syncthreads();
+    }
+    for (int e = tid; e < HD * HD; e += 256)
+        metric[(size_t)h * HD * HD + e] = __float2bfloat16_rn(Lm[(e >> 7) * 129 + (e & 127)]);
+}
+
+// ------------------------------------------------------------------------------------------------ probes
+// Probe i of a head = scale * mean of the query rows of 64-row block floor(i (nb - 1) / 63 + 0.5) (representatives.py:36-46).
+__global__ void __launch_bounds__(HD)
+probe_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ probes, int L, int H, int nb, float scale) {
+    const int i = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    const int blk = (int)((float)(i * (nb - 1)) / (float)(NP - 1) + 0.5f);
+    float s = 0.f;
+    int n = 0;
+    for (int r = 0; r < 64; ++r) {
+        const int row = blk * 64 + r;
+        if (row < L) { s += __bfloat162float(q[((size_t)row * H + h) * HD + d]); ++n; }
+    }
+    probes[((size_t)h * NP + i) * HD + d] = __float2bfloat16_rn(s * scale / fmaxf((float)n, 1.0f));
+}
+
+// ------------------------------------------------------------------------------------------------ k-means
+constexpr int KS = 130;           // bf16 row stride of the K tile (65 words: rows land in distinct banks)
+constexpr int XS = 129;           // float row stride of X and of the centroids
+constexpr int PS = 65;            // float row stride of the probe scores
+constexpr int KM_SMEM = 64 * KS * 2 + 64 * XS * 4 + 64 * PS * 4 + 4 * XS * 4 + 64 * 4 * 2 + 64;
+
+__global__ void __launch_bounds__(256)
+kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+              const __nv_bfloat16* __restrict__ metric, const __nv_bfloat16* __restrict__ probes,
+              __nv_bfloat16* __restrict__ k4, __nv_bfloat16* __restrict__ v4, float* __restrict__ c4,
+              __nv_bfloat16* __restrict__ km, __nv_bfloat16* __restrict__ vm, int L, int H, int nb4, int iters) {
+    extern __shared__ __align__(16) uint8_t raw[];
+    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(raw);                     // [64][KS]
+    float* sX = reinterpret_cast<float*>(raw + 64 * KS * 2);                        // [64][XS]
+    float* sP = sX + 64 * XS;                                                       // [64 probes][PS]
+    float* cen = sP + 64 * PS;                                                      // [4][XS]
+    float* w = cen + 4 * XS;                                                        // [64]
+    int* lab = reinterpret_cast<int*>(w + 64);                                      // [64]
+    __shared__ float cw[4];
+    __shared__ int s_changed;
+    __shared__ float s_cnt[4];
+    const int j = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int nvalid = min(L - j * 64, 64);
+
+    // K tile (rows past L are zero)
+    for (int e = tid; e < 64 * 16; e += 256) {
+        const int r = e >> 4, c16 = e & 15;
+        uint4 x = make_uint4(0, 0, 0, 0);
+        if (r < nvalid) x = *reinterpret_cast<const uint4*>(k + ((size_t)(j * 64 + r) * H + h) * HD + c16 * 8);
+        uint32_t* d = reinterpret_cast<uint32_t*>(sK + r * KS + c16 * 8);
+        d[0] = x.x; d[1] = x.y; d[2] = x.z; d[3] = x.w;
+    }
+    __syncthreads();
+
+    // X = K M (bf16 products, fp32 sums): thread -> rows 4 ty .., columns 8 tx ..
+    {
+        const int ty = tid >> 4, tx = tid & 15;
+        float acc[4][8];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 8; ++b) acc[a][b] = 0.f;
+        const __nv_bfloat16* mh = metric + (size_t)h * HD * HD + tx * 8;
+#pragma unroll 4
+        for (int kk = 0; kk < HD; ++kk) {
+            const uint4 mw = __ldg(reinterpret_cast<const uint4*>(mh + kk * HD));
+            const float mb[8] = {bf_lo(mw.x), bf_hi(mw.x), bf_lo(mw.y), bf_hi(mw.y),
+                                 bf_lo(mw.z), bf_hi(mw.z), bf_lo(mw.w), bf_hi(mw.w)};
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const float kv = __bfloat162float(sK[(4 * ty + a) * KS + kk]);
+#pragma unroll
+                for (int b = 0; b < 8; ++b) acc[a][b] = fmaf(kv, mb[b], acc[a][b]);
+            }
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 8; ++b) sX[(4 * ty + a) * XS + 8 * tx + b] = acc[a][b];
+    }
+    // probe scores: thread -> probes 4 py .., tokens 4 tx ..
+    {
+        const int py = tid >> 4, tx = tid & 15;
+        float acc[4][4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
+        const __nv_bfloat16* ph = probes + ((size_t)h * NP + 4 * py) * HD;
+        for (int d = 0; d < HD; d += 2) {
+            float pa[4][2], kb[4][2];
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const uint32_t pw = __ldg(reinterpret_cast<const uint32_t*>(ph + a * HD + d));
+                pa[a][0] = bf_lo(pw); pa[a][1] = bf_hi(pw);
+                const uint32_t kw = *reinterpret_cast<const uint32_t*>(sK + (4 * tx + a) * KS + d);
+                kb[a][0] = bf_lo(kw); kb[a][1] = bf_hi(kw);
+            }
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(pa[a][1], kb[b][1], fmaf(pa[a][0], kb[b][0], acc[a][b]));
+        }
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int b = 0; b < 4; ++b) sP[(4 * py + a) * PS + 4 * tx + b] = acc[a][b];
+    }
+    __syncthreads();
+    // each probe's softmax over the block's valid tokens (natural exponent)
+    if (tid < NP) {
+        float* row = sP + tid * PS;
+        float mx = -INFINITY;
+        for (int t = 0; t < nvalid; ++t) mx = fmaxf(mx, row[t]);
+        float sum = 0.f;
+        for (int t = 0; t < 64; ++t) {
+            const float e = t < nvalid ? expf(row[t] - mx) : 0.f;
+            row[t] = e;
+            sum += e;
+        }
+        const float inv = 1.0f / sum;
+        for (int t = 0; t < 64; ++t) row[t] *= inv;
+    }
+    __syncthreads();
+    if (tid < 64) {
+        float s = 0.f;
+        for (int p = 0; p < NP; ++p) s += sP[p * PS + tid];
+        w[tid] = tid < nvalid ? s * ((float)nvalid / (float)NP) : 0.f;
+        lab[tid] = tid >> 4;
+    }
+    __syncthreads();
+
+    // weighted centroids of the current labels; keep_old: an emptied cluster keeps its centroid
+    auto update_centroids = [&](bool keep_old) {
+        if (tid < 4) {
+            float s = 0.f;
+            for (int t = 0; t < nvalid; ++t) s += (lab[t] == tid) ? w[t] : 0.f;
+            cw[tid] = s;
+        }
+        __syncthreads();
+        for (int e = tid; e < 4 * HD; e += 256) {
+            const int c = e >> 7, d = e & 127;
+            float s = 0.f;
+            for (int t = 0; t < nvalid; ++t) s += (lab[t] == c) ? w[t] * sX[t * XS + d] : 0.f;
+            if (!keep_old || cw[c] > 0.f) cen[c * XS + d] = s / fmaxf(cw[c], 1e-6f);
+        }
+        __syncthreads();
+    };
+    update_centroids(false);
+    for (int it = 0; it < iters; ++it) {
+        // thread -> (token tid / 4, cluster tid % 4)
+        const int t = tid >> 2, c = tid & 3;
+        float dot = 0.f, cc = 0.f;
+        for (int d = 0; d < HD; ++d) {
+            const float cv = cen[c * XS + d];
+            dot = fmaf(sX[t * XS + d], cv, dot);
+            cc = fmaf(cv, cv, cc);
+        }
+        float dist = cw[c] > 0.f ? cc - 2.0f * dot : INFINITY;
+        int best = c;
+        // first minimum among the four clusters of this token (lanes 4 t' .. 4 t' + 3)
+#pragma unroll
+        for (int o = 1; o < 4; o <<= 1) {
+            const float od = __shfl_xor_sync(0xffffffffu, dist, o);
+            const int ob = __shfl_xor_sync(0xffffffffu, best, o);
+            if (od < dist || (od == dist && ob < best)) { dist = od; best = ob; }
+        }
+        if (tid == 0) s_changed = 0;
+        __syncthreads();
+        if (c == 0 && t < nvalid && best != lab[t]) atomicAdd(&s_changed, 1);
+        __syncthreads();
+        if (c == 0) lab[t] = best;
+        const int changed = s_changed;
+        __syncthreads();
+        update_centroids(true);
+        if (changed == 0) break;
+    }
+
+    // plain means of K and V over the final clusters, and the block means when asked for
+    if (tid < 4) {
+        int n = 0;
+        for (int t = 0; t < nvalid; ++t) n += lab[t] == tid;
+        s_cnt[tid] = (float)n;
+        c4[(size_t)h * nb4 + j * 4 + tid] = n > 0 ? log2f((float)n) : -INFINITY;
+    }
+    __syncthreads();
+    {
+        const int which = tid >> 7, d = tid & 127;
+        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int t = 0; t < nvalid; ++t) {
+            const float x = which ? __bfloat162float(v[((size_t)(j * 64 + t) * H + h) * HD + d])
+                                  : __bfloat162float(sK[t * KS + d]);
+            const int l = lab[t];
+            s[0] += l == 0 ? x : 0.f; s[1] += l == 1 ? x : 0.f; s[2] += l == 2 ? x : 0.f; s[3] += l == 3 ? x : 0.f;
+        }
+        __nv_bfloat16* o = (which ? v4 : k4) + ((size_t)h * nb4 + j * 4) * HD + d;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[c * HD] = __float2bfloat16_rn(s[c] * (1.0f / fmaxf(s_cnt[c], 1.0f)));
+        __nv_bfloat16* mo = which ? vm : km;
+        if (mo) mo[((size_t)j * H + h) * HD + d] = __float2bfloat16_rn(((s[0] + s[1]) + (s[2] + s[3])) / (float)nvalid);
+    }
+}
+
+}  // namespace es
+
+using namespace es;
+
+// Rows of q per Gram partial, as the reference splits them (representatives.py:160).
+static int gram_rows_per_split(int L) { return ((((L + 31) / 32) + 63) / 64) * 64; }
+
+extern "C" int es_reps_gram_splits(int32_t L) {
+    if (L <= 0) return 0;
+    const int rps = gram_rows_per_split(L);
+    return (L + rps - 1) / rps;
+}
+
+// q (L, H, 128) bf16 -> metric (H, 128, 128) bf16 (Cholesky factor) and probes (H, 64, 128) bf16.
+// gram_parts: scratch of es_reps_gram_splits(L) * H * 128 * 128 floats; gram (H, 128, 128) fp32 receives the
+// regularised Gram matrix when not null.
+extern "C" int es_reps_metric(const void* q, float* gram_parts, float* gram, void* metric, void* probes, int32_t L,
+                              int32_t H, void* stream) {
+    if (!q || !gram_parts || !metric || !probes) return set_error(-1, "es_reps_metric: null pointer");
+    if (L <= 0 || H <= 0) return set_error(-1, "es_reps_metric: L and H must be positive");
+    if ((uintptr_t)q & 15) return set_error(-1, "es_reps_metric: q must be 16-byte aligned");
+    const int nb = (L + 63) / 64;
+    const int rps = gram_rows_per_split(L), nsplit = (L + rps - 1) / rps;
+    cudaStream_t st = (cudaStream_t)stream;
+    gram_kernel<<<dim3(H, nsplit), 256, 0, st>>>((const __nv_bfloat16*)q, gram_parts, L, H, rps, nsplit);
+    ES_CHECK_LAUNCH("gram");
+    const int smem = (2 * HD * 129 + HD) * (int)sizeof(float);
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(metric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
+        attr = true;
+    }
+    const float scale = 1.0f / sqrtf((float)HD);
+    metric_kernel<<<H, 256, smem, st>>>(gram_parts, (__nv_bfloat16*)metric, gram, nsplit, scale * scale / (float)L);
+    ES_CHECK_LAUNCH("metric");
+    probe_kernel<<<dim3(NP, H), HD, 0, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)probes, L, H, nb, scale);
+    ES_CHECK_LAUNCH("probes");
+    return 0;
+}
+
+// k, v (L, H, 128) bf16 -> k_rep, v_rep (H, (nb + 1) * 4, 128) bf16 and log_counts (H, (nb + 1) * 4) fp32; block nb of
+// the tables is left as the caller initialised it (zeros, -inf). k_mean / v_mean (nb, H, 128) are written when given.
+extern "C" int es_reps_kmeans(const void* k, const void* v, const void* metric, const void* probes, void* k_rep,
+                              void* v_rep, float* log_counts, void* k_mean, void* v_mean, int32_t L, int32_t H,
+                              int32_t iters, void* stream) {
+    if (!k || !v || !metric || !probes || !k_rep || !v_rep || !log_counts)
+        return set_error(-1, "es_reps_kmeans: null pointer");
+    if (L <= 0 || H <= 0) return set_error(-1, "es_reps_kmeans: L and H must be positive");
+    if (((uintptr_t)k | (uintptr_t)metric) & 15) return set_error(-1, "es_reps_kmeans: k and metric must be 16-byte aligned");
+    if ((k_mean == nullptr) != (v_mean == nullptr)) return set_error(-1, "es_reps_kmeans: give both means or neither");
+    const int nb = (L + 63) / 64;
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(kmeans_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KM_SMEM);
+        if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
+        attr = true;
+    }
+    kmeans_kernel<<<dim3(nb, H), 256, KM_SMEM, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)metric, (const __nv_bfloat16*)probes,
+        (__nv_bfloat16*)k_rep, (__nv_bfloat16*)v_rep, log_counts, (__nv_bfloat16*)k_mean, (__nv_bfloat16*)v_mean, L, H,
+        (nb + 1) * 4, iters);
+    ES_CHECK_LAUNCH("kmeans");
+    return 0;
+}

@@ -1,0 +1,332 @@
+// The memory-bound kernels around the attention kernel: block means, per-tile scales, mass estimates of the skipped
+// blocks, and the block-mean compensation of fallback tiles. Vectorised 16-byte loads, warp shuffles, mma.sync for the
+// one small contraction (16 sampled query rows x block-mean keys).
+#include "es_api_internal.h"
+
+#include <cuda_bf16.h>
+#include <math.h>
+
+namespace es {
+
+constexpr int HD = 128;
+constexpr float LOG2E_F = 1.4426950408889634f;
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+
+// ------------------------------------------------------------------------------------------------ block means
+// Mean key and value of every 64-token block, (L, H, 128) -> (nb, H, 128); the tail block divides by its real length
+// (echosparse/kernels/triton_ops.py:21-40). One CTA per (block, head): thread = (row group of 4 rows, 16-byte column).
+__global__ void __launch_bounds__(256)
+block_mean_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                  __nv_bfloat16* __restrict__ km, __nv_bfloat16* __restrict__ vm, int L, int H) {
+    __shared__ float part[2][16][HD];
+    const int j = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int rg = tid >> 4, c16 = tid & 15;
+    float ak[8] = {0, 0, 0, 0, 0, 0, 0, 0}, av[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = j * 64 + i * 16 + rg;
+        if (row < L) {
+            const size_t off = ((size_t)row * H + h) * HD + c16 * 8;
+            const uint4 a = *reinterpret_cast<const uint4*>(k + off);
+            const uint4 b = *reinterpret_cast<const uint4*>(v + off);
+            ak[0] += bf16_lo(a.x); ak[1] += bf16_hi(a.x); ak[2] += bf16_lo(a.y); ak[3] += bf16_hi(a.y);
+            ak[4] += bf16_lo(a.z); ak[5] += bf16_hi(a.z); ak[6] += bf16_lo(a.w); ak[7] += bf16_hi(a.w);
+            av[0] += bf16_lo(b.x); av[1] += bf16_hi(b.x); av[2] += bf16_lo(b.y); av[3] += bf16_hi(b.y);
+            av[4] += bf16_lo(b.z); av[5] += bf16_hi(b.z); av[6] += bf16_lo(b.w); av[7] += bf16_hi(b.w);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        part[0][rg][c16 * 8 + e] = ak[e];
+        part[1][rg][c16 * 8 + e] = av[e];
+    }
+    __syncthreads();
+    const int which = tid >> 7, d = tid & 127;
+    float s = 0.f;
+#pragma unroll
+    for (int g = 0; g < 16; ++g) s += part[which][g][d];
+    const float n = (float)min(L - j * 64, 64);
+    (which ? vm : km)[((size_t)j * H + h) * HD + d] = __float2bfloat16_rn(s / n);
+}
+
+// ------------------------------------------------------------------------------------------------ full-step scales
+// After a step that computed every block (triton_ops.py:180-199): scale_exact = mean_rows 2^clamp(m - lse) / rows,
+// scale_skip = 1, and the padding rows of lse go back to 1e30.
+__global__ void __launch_bounds__(128)
+full_scale_kernel(const float* __restrict__ m, float* __restrict__ lse, float* __restrict__ scale_exact,
+                  float* __restrict__ scale_skip, int L, int H, int nq) {
+    __shared__ float part[4];
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int row = t * 128 + tid;
+    const bool rv = row < L;
+    const float nrows = (float)min(L - t * 128, 128);
+    const float ls = lse[(size_t)row * H + h];
+    if (!rv) lse[(size_t)row * H + h] = 1e30f;
+    float f = rv ? exp2f(fminf(fmaxf(m[(size_t)row * H + h] - ls, -100.f), 100.f)) : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) f += __shfl_xor_sync(0xffffffffu, f, o);
+    if ((tid & 31) == 0) part[tid >> 5] = f;
+    __syncthreads();
+    if (tid == 0) {
+        const float s = (part[0] + part[1]) + (part[2] + part[3]);
+        scale_exact[h * nq + t] = s / nrows / nrows;
+        scale_skip[h * nq + t] = 1.0f;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ estimates
+// Mass estimates of the skipped blocks for the next selection, and the per-tile scales (triton_ops.py:122-177):
+//   est[t, b] = mean over 16 sampled rows r = 128 t + 8 s of 2^min(c q_r.kmean_b - m_r + log2 len_b, 100), written into
+//   the map for blocks that were not kept; f = mean_rows 2^clamp(m - m_new); scale_exact = f / rows;
+//   scale_skip = f * clamp((sum_kept mass / rows) / sum_kept est, 1, 64).
+// One CTA (8 warps) per (tile, head); a warp takes 8 blocks at a time: S(16 x 8) by 8 mma.sync m16n8k16 over d.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(256)
+estimate_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ km,
+                const uint8_t* __restrict__ keep, const float* __restrict__ m, const float* __restrict__ mnew,
+                float* __restrict__ map, float* __restrict__ scale_exact, float* __restrict__ scale_skip,
+                float scale_log2, int L, int nb, float lb_last, int H, int nq) {
+    __shared__ float red[8][2];
+    __shared__ float fpart[8];
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tg = lane & 3;
+    // A fragments of the 16 sampled rows (row s -> query row 128 t + 8 s), all 8 k-steps
+    uint32_t afr[8][4];
+    const int r0 = t * 128 + 8 * g, r1 = t * 128 + 8 * (g + 8);
+    const bool v0 = r0 < L, v1 = r1 < L;
+    const __nv_bfloat16* q0 = q + ((size_t)r0 * H + h) * HD;
+    const __nv_bfloat16* q1 = q + ((size_t)r1 * H + h) * HD;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+        const int d = ks * 16 + tg * 2;
+        afr[ks][0] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
+        afr[ks][1] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
+        afr[ks][2] = v0 ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
+        afr[ks][3] = v1 ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
+    }
+    const float m0 = v0 ? m[(size_t)r0 * H + h] : 0.f, m1 = v1 ? m[(size_t)r1 * H + h] : 0.f;
+    int nsv = 0;
+    for (int s = 0; s < 16; ++s) nsv += (t * 128 + 8 * s) < L;
+    const float inv_ns = 1.0f / fmaxf((float)nsv, 1.0f);
+    const size_t mbase = ((size_t)h * nq + t) * nb;
+    float num = 0.f, den = 0.f;
+    for (int c0 = warp * 8; c0 < nb; c0 += 64) {
+        const int col = c0 + g;                       // B fragment: column n = lane / 4
+        const bool cv = col < nb;
+        const __nv_bfloat16* kr = km + ((size_t)(cv ? col : 0) * H + h) * HD;
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            const int d = ks * 16 + tg * 2;
+            const uint32_t b0 = cv ? *reinterpret_cast<const uint32_t*>(kr + d) : 0u;
+            const uint32_t b1 = cv ? *reinterpret_cast<const uint32_t*>(kr + d + 8) : 0u;
+            mma_bf16_16816(acc, afr[ks], b0, b1);
+        }
+        // acc[0], acc[1]: row g, columns c0 + 2 tg, + 1; acc[2], acc[3]: row g + 8
+        float e[2];
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+            const int cc = c0 + 2 * tg + x;
+            const float lb = (cc == nb - 1) ? lb_last : 6.0f;
+            const float e0 = v0 ? exp2f(fminf(acc[x] * scale_log2 - m0 + lb, 100.f)) : 0.f;
+            const float e1 = v1 ? exp2f(fminf(acc[2 + x] * scale_log2 - m1 + lb, 100.f)) : 0.f;
+            float s = e0 + e1;
+            s += __shfl_xor_sync(0xffffffffu, s, 4);
+            s += __shfl_xor_sync(0xffffffffu, s, 8);
+            s += __shfl_xor_sync(0xffffffffu, s, 16);
+            e[x] = s * inv_ns;
+        }
+        if (g == 0) {
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                const int cc = c0 + 2 * tg + x;
+                if (cc < nb) {
+                    if (keep[mbase + cc] != 0) {
+                        num += map[mbase + cc];
+                        den += e[x];
+                    } else {
+                        map[mbase + cc] = e[x];
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        num += __shfl_xor_sync(0xffffffffu, num, o);
+        den += __shfl_xor_sync(0xffffffffu, den, o);
+    }
+    // f over the tile's rows: threads 0..127
+    float f = 0.f;
+    if (tid < 128) {
+        const int row = t * 128 + tid;
+        if (row < L) {
+            const float a = m[(size_t)row * H + h], b = mnew[(size_t)row * H + h];
+            f = exp2f(fminf(fmaxf(a - b, -100.f), 100.f));
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) f += __shfl_xor_sync(0xffffffffu, f, o);
+    if (lane == 0) { red[warp][0] = num; red[warp][1] = den; fpart[warp] = f; }
+    __syncthreads();
+    if (tid == 0) {
+        const float nrows = (float)min(L - t * 128, 128);
+        float nn = 0.f, dd = 0.f;
+        for (int w = 0; w < 8; ++w) { nn += red[w][0]; dd += red[w][1]; }
+        const float ff = ((fpart[0] + fpart[1]) + (fpart[2] + fpart[3])) / nrows;
+        scale_exact[h * nq + t] = ff / nrows;
+        // The block-mean estimate underestimates block mass (Jensen): calibrate it on the blocks computed exactly.
+        nn /= nrows;
+        const float c = dd > 0.f ? fminf(fmaxf(nn / fmaxf(dd, 1e-30f), 1.0f), 64.0f) : 1.0f;
+        scale_skip[h * nq + t] = ff * c;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ compensation
+// Block-mean compensation of the skipped blocks for flagged tiles, in place (triton_ops.py:251-295):
+//   e_b = 2^min(c q.kmean_b - lse + log2 len_b, 100) over all blocks not kept;  out = (out + sum e v_b) / (1 + sum e);
+//   lse += log2(1 + sum e).  CTAs stride over the (tile, head) pairs; thread = row; the row's numerator lives in
+// shared memory with a padded stride so that the 128 rows hit distinct banks.
+constexpr int COMP_STRIDE = HD + 1;
+__global__ void __launch_bounds__(128)
+compensate_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ km,
+                  const __nv_bfloat16* __restrict__ vm, const uint8_t* __restrict__ keep, float* __restrict__ lse,
+                  __nv_bfloat16* __restrict__ out, const int* __restrict__ flags, float scale_log2, int L, int nb,
+                  float lb_last, int H, int nq) {
+    extern __shared__ float nu[];                    // [128][COMP_STRIDE]
+    const int tid = threadIdx.x;
+    for (int it = blockIdx.x; it < nq * H; it += gridDim.x) {
+        const int t = it / H, h = it % H;
+        if (flags[t * H + h] == 0) continue;
+        const int row = t * 128 + tid;
+        const bool rv = row < L;
+        uint32_t qr[64];
+        const __nv_bfloat16* qp = q + ((size_t)(rv ? row : 0) * H + h) * HD;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const uint4 w = *reinterpret_cast<const uint4*>(qp + 8 * i);
+            qr[4 * i] = w.x; qr[4 * i + 1] = w.y; qr[4 * i + 2] = w.z; qr[4 * i + 3] = w.w;
+        }
+        float* mine = nu + tid * COMP_STRIDE;
+        for (int d = 0; d < HD; ++d) mine[d] = 0.f;
+        const float ls = lse[(size_t)row * H + h];
+        float lu = 0.f;
+        const uint8_t* kp = keep + ((size_t)h * nq + t) * nb;
+        for (int b = 0; b < nb; ++b) {
+            if (kp[b] != 0) continue;                // uniform over the CTA
+            const uint4* kr = reinterpret_cast<const uint4*>(km + ((size_t)b * H + h) * HD);
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint4 w = __ldg(kr + i);
+                s = fmaf(bf16_lo(qr[4 * i]), bf16_lo(w.x), s); s = fmaf(bf16_hi(qr[4 * i]), bf16_hi(w.x), s);
+                s = fmaf(bf16_lo(qr[4 * i + 1]), bf16_lo(w.y), s); s = fmaf(bf16_hi(qr[4 * i + 1]), bf16_hi(w.y), s);
+                s = fmaf(bf16_lo(qr[4 * i + 2]), bf16_lo(w.z), s); s = fmaf(bf16_hi(qr[4 * i + 2]), bf16_hi(w.z), s);
+                s = fmaf(bf16_lo(qr[4 * i + 3]), bf16_lo(w.w), s); s = fmaf(bf16_hi(qr[4 * i + 3]), bf16_hi(w.w), s);
+            }
+            const float lb = (b == nb - 1) ? lb_last : 6.0f;
+            float e = exp2f(fminf(s * scale_log2 - ls + lb, 100.f));
+            e = rv ? e : 0.f;
+            lu += e;
+            const float eb = __bfloat162float(__float2bfloat16_rn(e));      // the reference rounds e to bf16 for e . v
+            const uint4* vr = reinterpret_cast<const uint4*>(vm + ((size_t)b * H + h) * HD);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint4 w = __ldg(vr + i);
+                float* p = mine + 8 * i;
+                p[0] = fmaf(eb, bf16_lo(w.x), p[0]); p[1] = fmaf(eb, bf16_hi(w.x), p[1]);
+                p[2] = fmaf(eb, bf16_lo(w.y), p[2]); p[3] = fmaf(eb, bf16_hi(w.y), p[3]);
+                p[4] = fmaf(eb, bf16_lo(w.z), p[4]); p[5] = fmaf(eb, bf16_hi(w.z), p[5]);
+                p[6] = fmaf(eb, bf16_lo(w.w), p[6]); p[7] = fmaf(eb, bf16_hi(w.w), p[7]);
+            }
+        }
+        if (rv) {
+            __nv_bfloat16* op = out + ((size_t)row * H + h) * HD;
+            const float inv = 1.0f / (1.0f + lu);
+#pragma unroll 4
+            for (int i = 0; i < 16; ++i) {
+                uint4 w = *reinterpret_cast<const uint4*>(op + 8 * i);
+                const float* p = mine + 8 * i;
+                __nv_bfloat162 r0 = __floats2bfloat162_rn((bf16_lo(w.x) + p[0]) * inv, (bf16_hi(w.x) + p[1]) * inv);
+                __nv_bfloat162 r1 = __floats2bfloat162_rn((bf16_lo(w.y) + p[2]) * inv, (bf16_hi(w.y) + p[3]) * inv);
+                __nv_bfloat162 r2 = __floats2bfloat162_rn((bf16_lo(w.z) + p[4]) * inv, (bf16_hi(w.z) + p[5]) * inv);
+                __nv_bfloat162 r3 = __floats2bfloat162_rn((bf16_lo(w.w) + p[6]) * inv, (bf16_hi(w.w) + p[7]) * inv);
+                w.x = *reinterpret_cast<uint32_t*>(&r0); w.y = *reinterpret_cast<uint32_t*>(&r1);
+                w.z = *reinterpret_cast<uint32_t*>(&r2); w.w = *reinterpret_cast<uint32_t*>(&r3);
+                *reinterpret_cast<uint4*>(op + 8 * i) = w;
+            }
+        }
+        lse[(size_t)row * H + h] = rv ? ls + log2f(1.0f + lu) : 1e30f;
+    }
+}
+
+}  // namespace es
+
+using namespace es;
+
+extern "C" int es_block_means(const void* k, const void* v, void* k_mean, void* v_mean, int32_t L, int32_t H,
+                              void* stream) {
+    if (!k || !v || !k_mean || !v_mean) return set_error(-1, "es_block_means: null pointer");
+    if (L <= 0 || H <= 0) return set_error(-1, "es_block_means: L and H must be positive");
+    if (((uintptr_t)k | (uintptr_t)v) & 15) return set_error(-1, "es_block_means: k and v must be 16-byte aligned");
+    const int nb = (L + 63) / 64;
+    block_mean_kernel<<<dim3(nb, H), 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (__nv_bfloat16*)k_mean, (__nv_bfloat16*)v_mean, L, H);
+    ES_CHECK_LAUNCH("block_means");
+    return 0;
+}
+
+extern "C" int es_full_step_scales(const float* offset, float* lse, float* scale_exact, float* scale_skip, int32_t L,
+                                   int32_t H, void* stream) {
+    if (!offset || !lse || !scale_exact || !scale_skip) return set_error(-1, "es_full_step_scales: null pointer");
+    if (L <= 0 || H <= 0) return set_error(-1, "es_full_step_scales: L and H must be positive");
+    const int nq = (L + 127) / 128;
+    full_scale_kernel<<<dim3(nq, H), 128, 0, (cudaStream_t)stream>>>(offset, lse, scale_exact, scale_skip, L, H, nq);
+    ES_CHECK_LAUNCH("full_step_scales");
+    return 0;
+}
+
+extern "C" int es_estimate_skipped(const void* q, const void* k_mean, const uint8_t* keep, const float* offset,
+                                   const float* lse, float* mass, float* scale_exact, float* scale_skip, int32_t L,
+                                   int32_t H, void* stream) {
+    if (!q || !k_mean || !keep || !offset || !lse || !mass || !scale_exact || !scale_skip)
+        return set_error(-1, "es_estimate_skipped: null pointer");
+    if (L <= 0 || H <= 0) return set_error(-1, "es_estimate_skipped: L and H must be positive");
+    const int nq = (L + 127) / 128, nb = (L + 63) / 64;
+    const int tail = L - (nb - 1) * 64;
+    estimate_kernel<<<dim3(nq, H), 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_mean, keep, offset, lse, mass, scale_exact, scale_skip,
+        LOG2E_F / sqrtf((float)HD), L, nb, log2f((float)tail), H, nq);
+    ES_CHECK_LAUNCH("estimate_skipped");
+    return 0;
+}
+
+extern "C" int es_compensate_fallback(const void* q, const void* k_mean, const void* v_mean, const uint8_t* keep,
+                                      float* lse, void* out, const int32_t* flags, int32_t L, int32_t H, void* stream) {
+    if (!q || !k_mean || !v_mean || !keep || !lse || !out || !flags)
+        return set_error(-1, "es_compensate_fallback: null pointer");
+    if (L <= 0 || H <= 0) return set_error(-1, "es_compensate_fallback: L and H must be positive");
+    const int nq = (L + 127) / 128, nb = (L + 63) / 64;
+    const int tail = L - (nb - 1) * 64;
+    const int smem = 128 * COMP_STRIDE * (int)sizeof(float);
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(compensate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
+        attr = true;
+    }
+    const int grid = nq * H < 1184 ? nq * H : 1184;
+    compensate_kernel<<<grid, 128, smem, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_mean, (const __nv_bfloat16*)v_mean, keep, lse,
+        (__nv_bfloat16*)out, flags, LOG2E_F / sqrtf((float)HD), L, nb, log2f((float)tail), H, nq);
+    ES_CHECK_LAUNCH("compensate_fallback");
+    return 0;
+}
