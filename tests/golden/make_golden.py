@@ -5,9 +5,10 @@ kernels are Triton. Triton ships a CPU interpreter (TRITON_INTERPRET=1) that exe
 numpy; this script drives the reference's kernel functions through it, in the order the reference's attention
 processor calls them (echosparse/attention.py:215-330), and stores their outputs.
 
-One fix is applied to the interpreter, not to the reference: Triton 3.6's interpreter keeps bf16 tensors as uint16 bit
-patterns and its `tl.dot` multiplies those patterns as integers; `_patched_dot` below converts bf16 operands to float32
-first (what the GPU does).
+Two fixes are applied to the interpreter, not to the reference, so that it computes what the GPU computes. Triton 3.6's
+interpreter keeps bf16 tensors as uint16 bit patterns, and (1) its `tl.dot` multiplies those patterns as integers:
+`_patched_dot` converts bf16 operands to float32 first; (2) its float32 -> bf16 cast truncates the mantissa:
+`_patched_cast` rounds to nearest even, as `cvt.rn.bf16.f32` does.
 
 Run from the repository root, in a container that has the reference checked out:
 
@@ -72,6 +73,18 @@ def main(reference_root):
         return interpreter.TensorHandle(np.matmul(_as_f32(a), _as_f32(b), dtype=d.data.dtype) + d.data, d.dtype.scalar)
 
     interpreter.InterpreterBuilder.create_dot = _patched_dot
+    _orig_cast = interpreter.InterpreterBuilder.cast_impl
+
+    def _patched_cast(self, src, dst_type):
+        import triton.language as tl
+        if src.dtype.scalar == tl.float32 and dst_type.scalar == tl.bfloat16:
+            bits = (to_bf16_values(src.data).view(np.uint32) >> 16).astype(np.uint16).reshape(src.data.shape)
+            return interpreter.TensorHandle(bits, dst_type.scalar)
+        return _orig_cast(self, src, dst_type)
+
+    interpreter.InterpreterBuilder.cast_impl = _patched_cast
+    interpreter.InterpreterBuilder.create_fp_to_fp = lambda self, src, dst_type, rounding_mode: \
+        _patched_cast(self, src, dst_type)
 
     from echosparse.kernels import sm120 as S
     from echosparse.kernels import triton_ops as T
