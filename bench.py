@@ -1,0 +1,330 @@
+"""Benchmark of the EchoSparse sparse-step attention layer on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+A step is one sparse-step attention layer: both CFG branches through `EchoSparseAttention.__call__` (select, block
+means, representatives, fused sparse attention, fallback, estimates). Default workload: the Wan2.1-14B 720p shape
+(2 branches x 40 heads x 75,600 tokens, 10 % of the blocks kept, ~0.5 % of the tiles pushed into the online-softmax
+fallback). With N GPUs the heads are sharded (both branches of a head on one GPU), no collective in the data path.
+Rank 0 prints one JSON line. Inputs are seeded synthetic activations (see `synthetic.py`).
+
+`--impl reference` times the CPU restatement of the same step (oracle/echosparse_ref.py) on the host cores, on a bounded
+sample of query tiles of the same workload.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from self_trainable_or_free_attn_b200 import synthetic  # noqa: E402
+
+CONFIG_IDS = {"cpu_small": 0, "wan_1_3b_480p": 1, "wan_14b_720p": 2, "hunyuan_720p": 3}
+FALLBACK_RATE = 0.005        # share of (tile, head) pairs whose Q is scaled by 3x
+FALLBACK_Q_SCALE = 3.0
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"tflops": float(d["bf16_tflops_sustained"]), "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line)
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) != 6 or not parts[0].isdigit():
+                continue
+            sm.append(int(parts[0]))
+            mx.append(int(parts[1]))
+            reasons.update(n for n, v in zip(self.NAMES, parts[2:]) if v == "Active")
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def inject_fallback(q, rate, scale, seed):
+    """Scales Q by `scale` on a seeded random share of (tile, head) pairs, in place. Returns the number chosen."""
+    _, L, H, _ = q.shape
+    nq = -(-L // 128)
+    g = torch.Generator().manual_seed(seed)
+    pick = (torch.rand(nq, H, generator=g) < rate).nonzero().tolist()
+    for t, h in pick:
+        q[0, 128 * t:128 * (t + 1), h] *= scale
+    return len(pick)
+
+
+def build_job(args, rank, world, device):
+    """Inputs of this rank's head shard, and an attention processor taken through the dense and the full step on the
+    previous step's (perturbed) inputs, so that the next call is a sparse step."""
+    from self_trainable_or_free_attn_b200.attention import EchoSparseAttention
+    grid, heads_all, branches, density, text = synthetic.WORKLOADS[args.workload]
+    cid = CONFIG_IDS[args.workload]
+    heads = synthetic.shard_heads(heads_all, rank, world)
+    attn = EchoSparseAttention(density=density, dense_steps=2, dense_layers=(), refine_iters=6,
+                               threshold=args.threshold, min_blocks=1)
+    for b in range(branches):
+        qp, kp, vp = synthetic.branch_qkv(grid, cid, b, heads, device, text, prev=True)
+        attn(qp, kp, vp, 0, b, layer=1)          # dense: log2 LSE of the perturbed inputs -> offset
+        attn(qp, kp, vp, 1, b, layer=1)          # full step: first mass map, exact LSE of the perturbed inputs
+        del qp, kp, vp
+    inputs, injected = [], 0
+    for b in range(branches):
+        q, k, v = synthetic.branch_qkv(grid, cid, b, heads, device, text)
+        injected += inject_fallback(q, FALLBACK_RATE, FALLBACK_Q_SCALE, seed=977 * cid + 31 * b + rank)
+        inputs.append((q, k, v))
+    return attn, inputs, heads, injected
+
+
+def run_steps(attn, inputs, first_step, n):
+    outs = None
+    for i in range(n):
+        outs = [attn(q, k, v, first_step + i, b, layer=1) for b, (q, k, v) in enumerate(inputs)]
+    return outs
+
+
+def layer_flops(attn, inputs):
+    """Algorithmic FLOP of one step on this rank: every branch uses branch 0's selection."""
+    st = attn._states[(0, 1)]
+    L = inputs[0][0].shape[1]
+    return len(inputs) * synthetic.step_flops(L, st.counts, st.blocks, st.refine, st.skip_bits)
+
+
+def cpu_sample(workload, budget_s, threads, repeats=1):
+    """Times the CPU restatement of the fused step (oracle/cpu_step.py) on a sample of query tiles of one head and one
+    branch of the workload, sized to about `budget_s` seconds. Returns ([TFLOP/s per repeat], description, seconds)."""
+    from oracle import cpu_step
+    cid = CONFIG_IDS[workload]
+    job = cpu_step.build_sample(workload, cid, 4)
+    per_tile = cpu_step.time_sample(job, threads) / len(job["tiles"])
+    n = max(4, min(job["nq"], int(budget_s / max(per_tile, 1e-4))))
+    if n != len(job["tiles"]):
+        job = cpu_step.build_sample(workload, cid, n)
+    secs = [cpu_step.time_sample(job, threads) for _ in range(repeats)]
+    desc = (f"{len(job['tiles'])} of {job['nq']} query tiles of one head of one branch, fused sparse step "
+            f"(oracle/echosparse_ref.py) with lists, means and representatives built on the CPU")
+    return [job["flop"] / s / 1e12 for s in secs], desc, sum(secs)
+
+
+def reference_arm(args, threads):
+    """The CPU restatement of the step on the host cores: every step is one pass over a bounded sample of query tiles;
+    throughput in the same unit, the layer time extrapolated from it."""
+    grid, heads_all, branches, density, text = synthetic.WORKLOADS[args.workload]
+    n = args.warmup + args.steps
+    vals, sample, _ = cpu_sample(args.workload, args.cpu_seconds / 2, threads, repeats=n)
+    vals = vals[args.warmup:]
+    value = statistics.median(vals)
+    nominal = {"wan_14b_720p": 29.98e12, "wan_1_3b_480p": 2.33e12, "hunyuan_720p": 25.67e12}.get(args.workload)
+    line = {"impl": "reference", "metric": "sparse_attn_effective_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": nominal / (value * 1e12) * 1e3 if nominal else None, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.workload, "tokens": synthetic.grid_tokens(grid) + text, "heads": heads_all,
+                       "branches": branches, "density": density,
+                       "step": "fused sparse step on host cores; ms_per_step extrapolates the sample's throughput to the "
+                               "layer's nominal algorithmic FLOP"},
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="wan_14b_720p", choices=sorted(synthetic.WORKLOADS))
+    ap.add_argument("--threshold", type=float, default=20.0,
+                    help="flag threshold on |log2 row sum| (the 3x Q injection moves row sums by 2^20..2^60)")
+    ap.add_argument("--cpu-seconds", type=float, default=12.0)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference" and rank != 0:
+        return
+    grid, heads_all, branches, density, text = synthetic.WORKLOADS[args.workload]
+    threads = os.cpu_count() or 1
+    if args.impl == "reference":
+        return reference_arm(args, threads)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU; there is no CPU fallback of the product path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+    from self_trainable_or_free_attn_b200 import _native
+    from self_trainable_or_free_attn_b200.kernels import sm100 as K
+
+    attn, inputs, heads, injected = build_job(args, rank, world, device)
+    L = inputs[0][0].shape[1]
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- warm-up, then the device-resident timed region
+    run_steps(attn, inputs, 2, args.warmup)
+    timer = K.KernelTimer(["sparse_attention"])
+    sampler = ClockSampler(local)
+    barrier()
+    K.set_kernel_timer(timer)
+    launches0 = _native.launch_count()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    run_steps(attn, inputs, 2 + args.warmup, args.steps)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    clocks = sampler.stop()
+    launches = _native.launch_count() - launches0
+    K.set_kernel_timer(None)
+    kernel_ms = timer.ms("sparse_attention")
+    status = _native.device_status()
+    flops_rank = layer_flops(attn, inputs)
+    flagged = int(attn._states[(0, 1)].flags.sum())
+
+    # ---- end to end: host buffers, H2D of q, k, v and D2H of the output inside the timed region, double-buffered
+    host_in = [[t.cpu().pin_memory() for t in qkv] for qkv in inputs]
+    host_out = [torch.empty(qkv[0].shape, dtype=torch.bfloat16).pin_memory() for qkv in inputs]
+    dev_in = [[torch.empty_like(t) for t in inputs[0]] for _ in range(2)]
+    copy_stream = torch.cuda.Stream()
+    main_stream = torch.cuda.current_stream()
+
+    def e2e_steps(first_step, n):
+        seq = [(first_step + i, b) for i in range(n) for b in range(branches)]
+        ready = [torch.cuda.Event() for _ in seq]
+        freed = [torch.cuda.Event() for _ in seq]
+        for j, (step, b) in enumerate(seq):
+            slot = j % 2
+            with torch.cuda.stream(copy_stream):
+                if j >= 2:
+                    copy_stream.wait_event(freed[j - 2])         # the slot's previous user has finished
+                for d, s in zip(dev_in[slot], host_in[b]):
+                    d.copy_(s, non_blocking=True)
+                ready[j].record(copy_stream)
+            main_stream.wait_event(ready[j])
+            out = attn(*dev_in[slot], step, b, layer=1)
+            freed[j].record(main_stream)
+            done = torch.cuda.Event()
+            done.record(main_stream)
+            with torch.cuda.stream(copy_stream):
+                copy_stream.wait_event(done)
+                host_out[b].copy_(out, non_blocking=True)
+                out.record_stream(copy_stream)
+        main_stream.wait_stream(copy_stream)
+
+    e2e_steps(2 + args.warmup + args.steps, 1)
+    barrier()
+    e0.record()
+    e2e_steps(3 + args.warmup + args.steps, args.steps)
+    e1.record()
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    h2d = sum(t.numel() * 2 for qkv in inputs for t in qkv)
+    d2h = sum(qkv[0].numel() * 2 for qkv in inputs)
+
+    # ---- whole-job numbers: max time over ranks, sum of work
+    stats = torch.tensor([ms, ms_e2e, flops_rank, float(launches), float(h2d), float(d2h), float(status),
+                          float(flagged), float(injected)], device=device, dtype=torch.float64)
+    if dist is not None:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, ms_e2e, status = float(mx[0]), float(mx[1]), int(mx[6])
+        flops_all, launches, h2d, d2h = float(sm[2]), int(sm[3]), int(sm[4]), int(sm[5])
+        flagged, injected = int(sm[7]), int(sm[8])
+    else:
+        flops_all = flops_rank
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+    if status != 0:
+        raise SystemExit(f"a kernel reported status {status}: a bounded wait gave up; the numbers are void")
+
+    peaks = measured_peaks()
+    ms_step = ms / args.steps
+    value = flops_all / (ms_step * 1e-3) / 1e12
+    k_ms = statistics.mean(kernel_ms)
+    k_flops = flops_rank / len(inputs)
+    achieved = k_flops / (k_ms * 1e-3) / 1e12
+    line = {
+        "metric": "sparse_attn_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "tokens": L, "heads": heads_all, "branches": branches, "density": density,
+                   "partition": f"heads over {world} GPU(s), both CFG branches of a head together",
+                   "step": "select + block means + representatives + fused sparse attention + fallback + estimates, "
+                           "both branches", "algorithmic_tflop_per_step": flops_all / 1e12,
+                   "l2": "inputs (q, k, v of a branch >> 126 MB) exceed L2 between iterations",
+                   "fallback_tiles_injected": injected, "fallback_tiles_flagged_last_step_branch0": flagged,
+                   "flag_threshold_log2": args.threshold},
+        "clocks": clocks,
+        "e2e": {"value": flops_all / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "roofline": {"bound": "tensor", "kernel": "attention_kernel<false> (es_sparse_attention)", "achieved": achieved,
+                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
+                     "peak_source": f"bf16_tflops_sustained of {peaks['source']}", "ms_per_launch": k_ms,
+                     "launches_timed": len(kernel_ms), "traffic": None},
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        tf, sample, dt = cpu_sample(args.workload, args.cpu_seconds, threads)
+        line["cpu_baseline"] = {"value": tf[0], "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample,
+                                "seconds": dt}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -22,6 +22,48 @@ def _cdiv(a, b):
     return -(-a // b)
 
 
+class KernelTimer:
+    """Optional CUDA-event timing of named kernel-set calls on the stream they launch on. Install with
+    `set_kernel_timer`; `ms(name)` returns the durations of the recorded calls (synchronises)."""
+
+    def __init__(self, names):
+        self.names = set(names)
+        self.events = {n: [] for n in names}
+
+    def ms(self, name):
+        torch.cuda.synchronize()
+        return [a.elapsed_time(b) for a, b in self.events[name]]
+
+    def clear(self):
+        for v in self.events.values():
+            v.clear()
+
+
+_timer = None
+
+
+def set_kernel_timer(timer):
+    global _timer
+    _timer = timer
+
+
+def _timed(fn):
+    name = fn.__name__
+
+    def wrapper(*args, **kwargs):
+        t = _timer
+        if t is None or name not in t.names:
+            return fn(*args, **kwargs)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        out = fn(*args, **kwargs)
+        b.record()
+        t.events[name].append((a, b))
+        return out
+    wrapper.__name__, wrapper.__doc__ = name, fn.__doc__
+    return wrapper
+
+
 def _cuda_bf16(*ts):
     for t in ts:
         assert t.is_cuda and t.dtype == torch.bfloat16 and t.is_contiguous(), "expects contiguous CUDA bf16 tensors"
@@ -33,6 +75,7 @@ def _lists(L, H, counts, blocks):
     assert blocks.dtype == torch.int32 and blocks.is_contiguous() and blocks.shape[:2] == (nq, H)
 
 
+@_timed
 def block_attention(q, k, v, out, counts, blocks, offset, lse, flags, mass=None, threshold=60.0):
     """Exact attention over a list of 64-token kv blocks with a fixed offset, plus per-block masses.
 
@@ -54,6 +97,7 @@ def block_attention(q, k, v, out, counts, blocks, offset, lse, flags, mass=None,
     return out
 
 
+@_timed
 def sparse_attention(q, k, v, k_mean, v_mean, skip_bits, out, counts, blocks, offset, lse, flags, refine, k_rep,
                      v_rep, log_counts, mass=None, threshold=60.0):
     """q, k, v, out: (L, H, 128) bf16. k_mean, v_mean: (nb, H, 128) block means. skip_bits: (H, nq, nw) int32 with
@@ -86,6 +130,7 @@ def sparse_attention(q, k, v, k_mean, v_mean, skip_bits, out, counts, blocks, of
     return out
 
 
+@_timed
 def exact_fallback(q, k, v, out, counts, blocks, lse, flags):
     """Online-softmax attention over the block list, for the tiles whose fixed offset was too far off."""
     L, H, hd = q.shape
@@ -97,6 +142,7 @@ def exact_fallback(q, k, v, out, counts, blocks, lse, flags):
             "exact_fallback")
 
 
+@_timed
 def compensate_fallback(q, k_mean, v_mean, keep, lse, out, flags):
     """Block-mean compensation of the skipped blocks for the fallback tiles, in place on `out` and `lse`."""
     L, H, hd = q.shape
@@ -107,6 +153,7 @@ def compensate_fallback(q, k_mean, v_mean, keep, lse, out, flags):
                                             N.ptr(flags), L, H, N.stream_ptr()), "compensate_fallback")
 
 
+@_timed
 def block_means(k, v, k_mean, v_mean):
     """Mean key and value of every 64-token block: (L, H, D) -> (nb, H, D)."""
     L, H, hd = k.shape
@@ -117,6 +164,7 @@ def block_means(k, v, k_mean, v_mean):
             "block_means")
 
 
+@_timed
 def select_blocks(mass, keep_prev, scale_exact, scale_skip, keep, counts, blocks, flags, skip_bits, refine, k, r, L,
                   sink=1 << 30):
     """Top-k blocks of every (query tile, head) by block probability, plus the forced ones.
@@ -135,6 +183,7 @@ def select_blocks(mass, keep_prev, scale_exact, scale_skip, keep, counts, blocks
                                       N.stream_ptr()), "select_blocks")
 
 
+@_timed
 def estimate_skipped(q, k_mean, keep, offset, lse, mass, scale_exact, scale_skip):
     """Mass estimates of the skipped blocks for the next step's selection, and the per-tile scales."""
     L, H, hd = q.shape
@@ -144,6 +193,7 @@ def estimate_skipped(q, k_mean, keep, offset, lse, mass, scale_exact, scale_skip
             "estimate_skipped")
 
 
+@_timed
 def full_step_scales(offset, lse, scale_exact, scale_skip, L):
     """Map scales after a step that computed every block; also resets the padding rows of `lse` to 1e30."""
     H, nq = scale_exact.shape
