@@ -105,25 +105,29 @@ def build_job(args, rank, world, device):
         attn(qp, kp, vp, 0, b, layer=1)          # dense: log2 LSE of the perturbed inputs -> offset
         attn(qp, kp, vp, 1, b, layer=1)          # full step: first mass map, exact LSE of the perturbed inputs
         del qp, kp, vp
+    # Two versions of every branch's Q that differ on a seeded 0.5 % of the (tile, head) pairs (Q scaled by 3 there).
+    # Steps alternate between them, so every step meets that share of tiles with an offset that is far off (in one
+    # direction or the other) and sends them through the online-softmax fallback.
     inputs, injected = [], 0
     for b in range(branches):
         q, k, v = synthetic.branch_qkv(grid, cid, b, heads, device, text)
-        injected += inject_fallback(q, FALLBACK_RATE, FALLBACK_Q_SCALE, seed=977 * cid + 31 * b + rank)
-        inputs.append((q, k, v))
+        q2 = q.clone()
+        injected += inject_fallback(q2, FALLBACK_RATE, FALLBACK_Q_SCALE, seed=977 * cid + 31 * b + rank)
+        inputs.append(((q, q2), k, v))
     return attn, inputs, heads, injected
 
 
 def run_steps(attn, inputs, first_step, n):
     outs = None
     for i in range(n):
-        outs = [attn(q, k, v, first_step + i, b, layer=1) for b, (q, k, v) in enumerate(inputs)]
+        outs = [attn(q[(first_step + i) & 1], k, v, first_step + i, b, layer=1) for b, (q, k, v) in enumerate(inputs)]
     return outs
 
 
 def layer_flops(attn, inputs):
     """Algorithmic FLOP of one step on this rank: every branch uses branch 0's selection."""
     st = attn._states[(0, 1)]
-    L = inputs[0][0].shape[1]
+    L = inputs[0][1].shape[1]
     return len(inputs) * synthetic.step_flops(L, st.counts, st.blocks, st.refine, st.skip_bits)
 
 
@@ -168,12 +172,11 @@ def reference_arm(args, threads):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="wan_14b_720p", choices=sorted(synthetic.WORKLOADS))
-    ap.add_argument("--threshold", type=float, default=20.0,
-                    help="flag threshold on |log2 row sum| (the 3x Q injection moves row sums by 2^20..2^60)")
+    ap.add_argument("--threshold", type=float, default=60.0, help="flag threshold on |log2 row sum| (reference: 60)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
@@ -201,7 +204,7 @@ def main():
     from self_trainable_or_free_attn_b200.kernels import sm100 as K
 
     attn, inputs, heads, injected = build_job(args, rank, world, device)
-    L = inputs[0][0].shape[1]
+    L = inputs[0][1].shape[1]
 
     def barrier():
         if dist is not None:
@@ -229,12 +232,12 @@ def main():
     kernel_ms = timer.ms("sparse_attention")
     status = _native.device_status()
     flops_rank = layer_flops(attn, inputs)
-    flagged = int(attn._states[(0, 1)].flags.sum())
+    flagged = int(attn._states[(0, 1)].flags.sum())          # branch 0, last timed step
 
     # ---- end to end: host buffers, H2D of q, k, v and D2H of the output inside the timed region, double-buffered
-    host_in = [[t.cpu().pin_memory() for t in qkv] for qkv in inputs]
-    host_out = [torch.empty(qkv[0].shape, dtype=torch.bfloat16).pin_memory() for qkv in inputs]
-    dev_in = [[torch.empty_like(t) for t in inputs[0]] for _ in range(2)]
+    host_in = [[[t.cpu().pin_memory() for t in q], k.cpu().pin_memory(), v.cpu().pin_memory()] for q, k, v in inputs]
+    host_out = [torch.empty(k.shape, dtype=torch.bfloat16).pin_memory() for _, k, _ in inputs]
+    dev_in = [[torch.empty_like(inputs[0][1]) for _ in range(3)] for _ in range(2)]
     copy_stream = torch.cuda.Stream()
     main_stream = torch.cuda.current_stream()
 
@@ -247,7 +250,8 @@ def main():
             with torch.cuda.stream(copy_stream):
                 if j >= 2:
                     copy_stream.wait_event(freed[j - 2])         # the slot's previous user has finished
-                for d, s in zip(dev_in[slot], host_in[b]):
+                hq, hk, hv = host_in[b]
+                for d, s in zip(dev_in[slot], (hq[step & 1], hk, hv)):
                     d.copy_(s, non_blocking=True)
                 ready[j].record(copy_stream)
             main_stream.wait_event(ready[j])
@@ -268,8 +272,8 @@ def main():
     e1.record()
     barrier()
     ms_e2e = e0.elapsed_time(e1)
-    h2d = sum(t.numel() * 2 for qkv in inputs for t in qkv)
-    d2h = sum(qkv[0].numel() * 2 for qkv in inputs)
+    h2d = sum(3 * k.numel() * 2 for _, k, _ in inputs)
+    d2h = sum(k.numel() * 2 for _, k, _ in inputs)
 
     # ---- whole-job numbers: max time over ranks, sum of work
     stats = torch.tensor([ms, ms_e2e, flops_rank, float(launches), float(h2d), float(d2h), float(status),

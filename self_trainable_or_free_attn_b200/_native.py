@@ -33,6 +33,8 @@ SIGNATURES = {
     "es_reps_gram_splits": [_I],
     "es_reps_metric": [_P, _P, _P, _P, _P, _I, _I, _P],
     "es_reps_kmeans": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "es_debug_set_trace": [_P],
+    "es_debug_trace_words": [],
 }
 _RESTYPES = {"es_last_error": ctypes.c_char_p, "es_launch_count": ctypes.c_longlong}
 

@@ -29,19 +29,18 @@ constexpr int HD = 128;       // head dim
 constexpr int NTHREADS = 192;
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t O_COL = 128;
+constexpr int NSLOT = 5;      // K/V tiles in flight per CTA (two CTAs share an SM's shared memory)
 
 constexpr uint32_t Q_BYTES = BM * HD * 2;        // 32 KB: [d half][128 rows][64 d] 128B-swizzled
 constexpr uint32_t KV_BYTES = BK * HD * 2;       // 16 KB: [d half][64 rows][64 d]
 constexpr uint32_t SMEM_Q = 0;
-constexpr uint32_t SMEM_K = SMEM_Q + Q_BYTES;            // 2 slots
-constexpr uint32_t SMEM_V = SMEM_K + 2 * KV_BYTES;       // 2 slots
-constexpr uint32_t SMEM_CTL = SMEM_V + 2 * KV_BYTES;     // barriers and small scratch
-constexpr uint32_t SMEM_TOTAL = SMEM_CTL + 512;
-constexpr uint32_t SMEM_ALLOC = SMEM_TOTAL + 1024;       // slack to align the base to 1024 B
+constexpr uint32_t SMEM_RING = SMEM_Q + Q_BYTES;                 // NSLOT tiles, K or V
+constexpr uint32_t SMEM_CTL = SMEM_RING + NSLOT * KV_BYTES;      // barriers and small scratch
+constexpr uint32_t SMEM_ALLOC = SMEM_CTL + 512;
 
 struct Ctl {
     uint64_t qfull;
-    uint64_t kfull[2], kempty[2], vfull[2], vempty[2];
+    uint64_t full[NSLOT], empty[NSLOT];
     uint64_t sfull[2], pfull[2];
     uint64_t ofull, drain;
     uint64_t massbar, flagbar;     // softmax warps' lane 0 -> the thread that adds their partial results
@@ -75,7 +74,16 @@ struct AttnArgs {
     float tail_log2;             // log2(tail_valid)
     int nvirt, nref;             // mean iterations (128 blocks each), refine iterations (32 list entries each)
     int* status;
+    uint32_t* trace;             // optional clock trace of the first CTAs (null: off); see es_debug_set_trace
 };
+
+// Clock trace for pipeline debugging: CTAs 0 .. TRACE_CTAS-1, softmax thread 0 (role 0) and the MMA thread (role 1),
+// the first TRACE_ITERS iterations, both halves, 8 time stamps each (clock cycles since the CTA started).
+constexpr int TRACE_CTAS = 8, TRACE_ITERS = 64;
+__device__ __forceinline__ void trace_put(uint32_t* tr, int role, int i, int x, int k, long long t0) {
+    if (tr != nullptr && blockIdx.x < TRACE_CTAS && i < TRACE_ITERS)
+        tr[((((size_t)blockIdx.x * 2 + role) * TRACE_ITERS + i) * 2 + x) * 8 + k] = (uint32_t)(clock64() - t0);
+}
 
 // K-major operand tile [d half][rows][64]: 8-row groups 1024 B apart; k step ks (16 elements) of the MMA.
 __device__ __forceinline__ uint64_t kmajor_desc(uint32_t base, uint32_t half_bytes, int ks) {
@@ -105,12 +113,39 @@ __device__ __forceinline__ void gather_slot(uint32_t slot, const __nv_bfloat16* 
     if (lane == 0) mbar_arrive(bar);
 }
 
+// p = 2^x for a pair of columns. MUFU computes 16 exponentials per clock and SM, as many clocks as the tensor cores need
+// for the same tile, so a share of the pairs (EMU) is computed on the FMA pipe instead: x = n + f with n = floor(x),
+// 2^f by a degree-4 polynomial (relative error 3e-6, far below the bf16 rounding of P), n added to the exponent field.
+__device__ __forceinline__ float2 exp2_pair_mufu(float2 x) { return make_float2(ex2_approx(x.x), ex2_approx(x.y)); }
+__device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
+    const float M = 12582912.0f;                               // 2^23 + 2^22: the integer part lands in the low mantissa bits
+    x.x = fmaxf(x.x, -126.0f);
+    x.y = fmaxf(x.y, -126.0f);
+    const float2 t = __fadd2_rd(x, make_float2(M, M));         // rounded down: f stays in [0, 1)
+    const float2 n = __fadd2_rn(t, make_float2(-M, -M));
+    const float2 f = __fadd2_rn(x, make_float2(-n.x, -n.y));
+    float2 p = make_float2(0.013426586054265499f, 0.013426586054265499f);
+    p = __ffma2_rn(p, f, make_float2(0.05224263295531273f, 0.05224263295531273f));
+    p = __ffma2_rn(p, f, make_float2(0.24128012359142303f, 0.24128012359142303f));
+    p = __ffma2_rn(p, f, make_float2(0.6930448412895203f, 0.6930448412895203f));
+    p = __ffma2_rn(p, f, make_float2(1.0f, 1.0f));
+    p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+    p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+    return p;
+}
+// Pair j (columns 2j, 2j+1) of a 64-column half goes to the FMA pipe when bit (j & 3) of EMU_PATTERN is set.
+#ifndef ES_EMU_PATTERN
+#define ES_EMU_PATTERN 0x5
+#endif
+__device__ __forceinline__ constexpr bool emulate_pair(int j) { return (ES_EMU_PATTERN >> (j & 3)) & 1; }
+
 template <bool FALLBACK>
 __global__ void __launch_bounds__(NTHREADS, 2)
 attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmKm,
                  const __grid_constant__ CUtensorMap tmVm, const AttnArgs a) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const long long t_start = clock64();
     // adjacent CTAs are adjacent query tiles of one head: their kv lists overlap in L2
     const int qb = blockIdx.x % a.nq, h = blockIdx.x / a.nq;
     const int th_idx = qb * a.H + h;
@@ -118,19 +153,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         if (a.flags[th_idx] == 0) return;          // uniform over the CTA, before anything is allocated
     }
 
-    extern __shared__ uint8_t smem_raw[];
-    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + (base - smem_u32(smem_raw)) + SMEM_CTL);
-    const uint32_t sQ = base + SMEM_Q, sK = base + SMEM_K, sV = base + SMEM_V;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + SMEM_CTL);
+    const uint32_t sQ = base + SMEM_Q, sRing = base + SMEM_RING;
     volatile int* abort_flag = &ctl->abort;
 
     if (tid == 0) {
+        if (base & 1023u) atomicCAS(a.status, 0, 901);   // the swizzled tiles need a 1024-byte aligned base
         mbar_init(smem_u32(&ctl->qfull), 1);
+        for (int i = 0; i < NSLOT; ++i) {
+            mbar_init(smem_u32(&ctl->full[i]), 1);
+            mbar_init(smem_u32(&ctl->empty[i]), 1);
+        }
         for (int i = 0; i < 2; ++i) {
-            mbar_init(smem_u32(&ctl->kfull[i]), 1);
-            mbar_init(smem_u32(&ctl->kempty[i]), 1);
-            mbar_init(smem_u32(&ctl->vfull[i]), 1);
-            mbar_init(smem_u32(&ctl->vempty[i]), 1);
             mbar_init(smem_u32(&ctl->sfull[i]), 1);
             mbar_init(smem_u32(&ctl->pfull[i]), 128);
         }
@@ -138,7 +174,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_init(smem_u32(&ctl->drain), 1);
         mbar_init(smem_u32(&ctl->massbar), 4);
         mbar_init(smem_u32(&ctl->flagbar), 4);
-        ctl->abort = 0;
+        ctl->abort = (base & 1023u) ? 1 : 0;
         mbar_fence_init();
         fence_proxy_async_smem();
     }
@@ -158,10 +194,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int nt = n + nvirt + nref;
     const int* list = a.blocks + (size_t)th_idx * a.nk;
 
-    uint32_t uK[2] = {0, 0}, uV[2] = {0, 0};          // producer: loads issued per slot (used again at teardown)
+    // K and V tiles travel through one ring of NSLOT slots in the order the MMA warp consumes them:
+    //   [fallback sweep: Ka(0) Kb(0) Ka(1) Kb(1) ...]  Ka(0) Kb(0)  { Va(i) Ka(i+1) Vb(i) Kb(i+1) } for i = 0 .. nt-1
+    // tile number `seq` lives in slot seq % NSLOT; its barriers are in phase (seq / NSLOT) & 1.
+    uint32_t pseq = 0;                                // producer: tiles issued (used again at teardown)
 
     if (warp == 5) {
-        // ------------------------------------------------------------ loads
+        // ------------------------------------------------------------ loads (all lanes walk the sequence together)
         bool ok = true;
         if (lane == 0) {
             tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV);
@@ -169,81 +208,77 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             tma_load_3d(sQ, &tmQ, smem_u32(&ctl->qfull), 0, qb * BM, h);
             tma_load_3d(sQ + Q_BYTES / 2, &tmQ, smem_u32(&ctl->qfull), 64, qb * BM, h);
         }
-        auto load_tile = [&](const CUtensorMap* m, uint32_t slot, uint64_t* full, uint64_t* empty, uint32_t& uses,
-                             int row) {
-            // lane 0 only
-            ok = ok && mbar_wait(smem_u32(empty), (uses & 1) ^ 1, abort_flag, a.status, 101);
+        const __nv_bfloat16* krep = a.k_rep + (size_t)h * a.nb4 * HD;
+        const __nv_bfloat16* vrep = a.v_rep + (size_t)h * a.nb4 * HD;
+        const int* rl = a.refine + (size_t)th_idx * a.rw;
+        // tile of iteration i, half x: K (is_v = false) or V
+        auto put = [&](int i, int x, bool is_v) {
             if (!ok) return;
-            mbar_arrive_expect_tx(smem_u32(full), KV_BYTES);
-            tma_load_3d(slot, m, smem_u32(full), 0, row, h);
-            tma_load_3d(slot + KV_BYTES / 2, m, smem_u32(full), 64, row, h);
-            ++uses;
+            const uint32_t slot = pseq % NSLOT, par = ((pseq / NSLOT) & 1) ^ 1;
+            if (lane == 0) ok = mbar_wait(smem_u32(&ctl->empty[slot]), par, abort_flag, a.status, 101);
+            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;     // the other lanes sleep at the shuffle instead of polling
+            if (!ok) return;
+            const uint32_t dst = sRing + slot * KV_BYTES, bar = smem_u32(&ctl->full[slot]);
+            if (i < n + nvirt) {
+                if (lane == 0) {
+                    int row;
+                    const CUtensorMap* m;
+                    if (i < n) {
+                        const int e = 2 * i + x;
+                        row = list[e < n64 ? e : e - 1] * BK;           // odd list: block a again, masked in the softmax
+                        m = is_v ? &tmV : &tmK;
+                    } else {
+                        row = (i - n) * 128 + 64 * x;                   // rows of the block-mean tables
+                        m = is_v ? &tmVm : &tmKm;
+                    }
+                    mbar_arrive_expect_tx(bar, KV_BYTES);
+                    tma_load_3d(dst, m, bar, 0, row, h);
+                    tma_load_3d(dst + KV_BYTES / 2, m, bar, 64, row, h);
+                }
+            } else {
+                // refine iteration: list entry 32 c + e fills columns 4e .. 4e+3 of the 128-column tile
+                const int my = rl[32 * (i - n - nvirt) + lane];
+                gather_slot(dst, is_v ? vrep : krep, my, x, lane, bar);
+            }
+            ++pseq;
         };
         if (FALLBACK) {
-            if (lane == 0) {
-                for (int i = 0; i < n && ok; ++i) {
-                    const int ba = list[2 * i];
-                    const int bb = (2 * i + 1 < n64) ? list[2 * i + 1] : ba;
-                    load_tile(&tmK, sK, &ctl->kfull[0], &ctl->kempty[0], uK[0], ba * BK);
-                    load_tile(&tmK, sK + KV_BYTES, &ctl->kfull[1], &ctl->kempty[1], uK[1], bb * BK);
-                }
-            }
+            for (int i = 0; i < n; ++i) { put(i, 0, false); put(i, 1, false); }
         }
-        if (lane == 0) {
-            for (int i = 0; i < n + nvirt && ok; ++i) {
-                int ra, rb;
-                const CUtensorMap *mk, *mv;
-                if (i < n) {
-                    const int ba = list[2 * i];
-                    const int bb = (2 * i + 1 < n64) ? list[2 * i + 1] : ba;   // odd list: block a again, masked
-                    ra = ba * BK; rb = bb * BK; mk = &tmK; mv = &tmV;
-                } else {
-                    ra = (i - n) * 128; rb = ra + 64; mk = &tmKm; mv = &tmVm;  // rows of the block-mean tables
-                }
-                load_tile(mk, sK, &ctl->kfull[0], &ctl->kempty[0], uK[0], ra);
-                load_tile(mk, sK + KV_BYTES, &ctl->kfull[1], &ctl->kempty[1], uK[1], rb);
-                load_tile(mv, sV, &ctl->vfull[0], &ctl->vempty[0], uV[0], ra);
-                load_tile(mv, sV + KV_BYTES, &ctl->vfull[1], &ctl->vempty[1], uV[1], rb);
-            }
-        }
-        if (nref > 0) {
-            // refine iterations: list entry 32c + e fills columns 4e .. 4e+3 of the 128-column tile
-            ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-            for (int x = 0; x < 2; ++x) {
-                uK[x] = __shfl_sync(0xffffffffu, uK[x], 0);
-                uV[x] = __shfl_sync(0xffffffffu, uV[x], 0);
-            }
-            const __nv_bfloat16* kt = a.k_rep + (size_t)h * a.nb4 * HD;
-            const __nv_bfloat16* vt = a.v_rep + (size_t)h * a.nb4 * HD;
-            const int* rl = a.refine + (size_t)th_idx * a.rw;
-            for (int c = 0; c < nref && ok; ++c) {
-                const int my = rl[32 * c + lane];
-                for (int x = 0; x < 2 && ok; ++x) {
-                    ok = mbar_wait(smem_u32(&ctl->kempty[x]), (uK[x] & 1) ^ 1, abort_flag, a.status, 102);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (ok) { gather_slot(sK + x * KV_BYTES, kt, my, x, lane, smem_u32(&ctl->kfull[x])); ++uK[x]; }
-                }
-                for (int x = 0; x < 2 && ok; ++x) {
-                    ok = mbar_wait(smem_u32(&ctl->vempty[x]), (uV[x] & 1) ^ 1, abort_flag, a.status, 103);
-                    ok = __all_sync(0xffffffffu, ok);
-                    if (ok) { gather_slot(sV + x * KV_BYTES, vt, my, x, lane, smem_u32(&ctl->vfull[x])); ++uV[x]; }
-                }
-            }
+        if (nt > 0) { put(0, 0, false); put(0, 1, false); }
+        for (int i = 0; i < nt; ++i) {
+            put(i, 0, true);
+            if (i + 1 < nt) put(i + 1, 0, false);
+            put(i, 1, true);
+            if (i + 1 < nt) put(i + 1, 1, false);
         }
     } else if (warp == 4) {
-        // ------------------------------------------------------------ MMAs (one thread)
-        if (lane == 0) {
+        // ------------------------------------------------------------ MMAs: the warp runs uniformly, one elected lane issues
+        {
             constexpr uint32_t IDESC_QK = umma_idesc_bf16(BM, BK, 0);
             constexpr uint32_t IDESC_PV = umma_idesc_bf16(BM, HD, 1);
-            uint32_t cK[2] = {0, 0}, cV[2] = {0, 0}, nQK[2] = {0, 0}, wP[2] = {0, 0};
+            // Shared-memory descriptors: everything but the start address is a constant of the layout, so the words are
+            // built once and an MMA costs one add. K-major (Q, K): LBO 16, SBO 1024; MN-major (V): LBO = half tile, SBO 1024.
+            const uint64_t dk0 = umma_desc_sw128(0, 16, 1024), dv0 = umma_desc_sw128(0, KV_BYTES / 2, 1024);
+            const uint32_t k_hi = (uint32_t)(dk0 >> 32), k_lo0 = (uint32_t)dk0;
+            const uint32_t v_hi = (uint32_t)(dv0 >> 32), v_lo0 = (uint32_t)dv0;
+            uint32_t q_lo[HD / 16];
+#pragma unroll
+            for (int ks = 0; ks < HD / 16; ++ks)
+                q_lo[ks] = k_lo0 + ((sQ + (uint32_t)(ks >> 2) * (Q_BYTES / 2) + (uint32_t)(ks & 3) * 32) >> 4);
+            uint32_t cseq = 0, nQK[2] = {0, 0}, wP[2] = {0, 0};
             bool ok = mbar_wait(smem_u32(&ctl->qfull), 0, abort_flag, a.status, 201);
+            auto take = [&](bool gathered) -> uint32_t {
+                const uint32_t slot = cseq % NSLOT;
+                ok = ok && mbar_wait(smem_u32(&ctl->full[slot]), (cseq / NSLOT) & 1, abort_flag, a.status, 202);
+                ++cseq;
+                if (gathered) fence_proxy_async_smem();    // cp.async gathers are generic-proxy writes
+                return slot;
+            };
             // S of half x <- Q K_x^T. The S columns also hold the previous P of that half: every earlier use must have
             // been handed back by the softmax warps (pfull) before they are overwritten.
             auto issue_qk = [&](int x, bool gathered) {
-                ok = ok && mbar_wait(smem_u32(&ctl->kfull[x]), cK[x] & 1, abort_flag, a.status, 202);
-                if (!ok) return;
-                ++cK[x];
-                if (gathered) fence_proxy_async_smem();    // cp.async gathers are generic-proxy writes
+                const uint32_t slot = take(gathered);
                 while (ok && wP[x] < nQK[x]) {
                     ok = mbar_wait(smem_u32(&ctl->pfull[x]), wP[x] & 1, abort_flag, a.status, 203);
                     ++wP[x];
@@ -251,12 +286,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 if (!ok) return;
                 tc_fence_after();
                 const uint32_t d = tmem + (uint32_t)x * BK;
-                const uint32_t kb = sK + (uint32_t)x * KV_BYTES;
+                const uint32_t kb_lo = k_lo0 + ((sRing + slot * KV_BYTES) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < HD / 16; ++ks)
-                    umma_ss(d, kmajor_desc(sQ, Q_BYTES / 2, ks), kmajor_desc(kb, KV_BYTES / 2, ks), IDESC_QK, ks > 0);
-                umma_commit(smem_u32(&ctl->sfull[x]));
-                umma_commit(smem_u32(&ctl->kempty[x]));
+                    if (elect_one()) umma_ss_lohi(d, q_lo[ks], k_hi, kb_lo + (uint32_t)(((ks >> 2) * (KV_BYTES / 2) + (ks & 3) * 32) >> 4), k_hi,
+                                 IDESC_QK, ks > 0);
+                if (elect_one()) umma_commit(smem_u32(&ctl->sfull[x]));
+                if (elect_one()) umma_commit(smem_u32(&ctl->empty[slot]));
                 ++nQK[x];
             };
             if (FALLBACK) {
@@ -268,28 +304,48 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             }
             for (int i = 0; i < nt && ok; ++i) {
                 const bool gat = i >= n + nvirt, nxg = i + 1 >= n + nvirt;
-                for (int x = 0; x < 2 && ok; ++x) {
-                    ok = mbar_wait(smem_u32(&ctl->vfull[x]), cV[x] & 1, abort_flag, a.status, 204);
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
                     if (!ok) break;
-                    ++cV[x];
-                    if (gat) fence_proxy_async_smem();
-                    ok = mbar_wait(smem_u32(&ctl->pfull[x]), wP[x] & 1, abort_flag, a.status, 205);   // P_x(i) stored
+                    if (lane == 0) trace_put(a.trace, 1, i, x, 0, t_start);
+                    const uint32_t slot = take(gat);
+                    if (lane == 0) trace_put(a.trace, 1, i, x, 1, t_start);
+                    ok = ok && mbar_wait(smem_u32(&ctl->pfull[x]), wP[x] & 1, abort_flag, a.status, 205);   // P_x(i) stored
+                    if (lane == 0) trace_put(a.trace, 1, i, x, 2, t_start);
                     if (!ok) break;
                     ++wP[x];
                     tc_fence_after();
                     const uint32_t p = tmem + (uint32_t)x * BK;            // bf16 pairs over the first 32 S columns
-                    const uint32_t vb = sV + (uint32_t)x * KV_BYTES;
+                    const uint32_t vb_lo = v_lo0 + ((sRing + slot * KV_BYTES) >> 4);
 #pragma unroll
                     for (int ks = 0; ks < BK / 16; ++ks)
-                        umma_ts(tmem + O_COL, p + ks * 8, mnmajor_desc(vb, KV_BYTES / 2, ks), IDESC_PV,
-                                (i > 0 || x > 0 || ks > 0) ? 1u : 0u);
-                    umma_commit(smem_u32(&ctl->vempty[x]));
-                    if (i + 1 == nt && x == 1) umma_commit(smem_u32(&ctl->ofull));
-                    if (i + 1 < nt) issue_qk(x, nxg);
+                        if (elect_one()) umma_ts_lohi(tmem + O_COL, p + ks * 8, vb_lo + (uint32_t)((ks * 2048) >> 4), v_hi, IDESC_PV,
+                                     (i > 0 || x > 0 || ks > 0) ? 1u : 0u);
+                    if (elect_one()) umma_commit(smem_u32(&ctl->empty[slot]));
+                    if (i + 1 == nt && x == 1) if (elect_one()) umma_commit(smem_u32(&ctl->ofull));
+                    if (lane == 0) trace_put(a.trace, 1, i, x, 3, t_start);
+                    if (i + 1 < nt) {
+                        const uint32_t kslot = take(nxg);
+                        if (lane == 0) trace_put(a.trace, 1, i, x, 4, t_start);
+                        // P_x(i) was waited for above, so S_x is free again
+                        const uint32_t d = tmem + (uint32_t)x * BK;
+                        const uint32_t kb_lo = k_lo0 + ((sRing + kslot * KV_BYTES) >> 4);
+                        if (ok) {
+#pragma unroll
+                            for (int ks = 0; ks < HD / 16; ++ks)
+                                if (elect_one()) umma_ss_lohi(d, q_lo[ks], k_hi,
+                                             kb_lo + (uint32_t)(((ks >> 2) * (KV_BYTES / 2) + (ks & 3) * 32) >> 4), k_hi,
+                                             IDESC_QK, ks > 0);
+                            if (elect_one()) umma_commit(smem_u32(&ctl->sfull[x]));
+                            if (elect_one()) umma_commit(smem_u32(&ctl->empty[kslot]));
+                            ++nQK[x];
+                        }
+                    }
+                    if (lane == 0) trace_put(a.trace, 1, i, x, 5, t_start);
                 }
             }
             // every MMA issued above has finished before tensor memory is freed
-            umma_commit(smem_u32(&ctl->drain));
+            if (elect_one()) umma_commit(smem_u32(&ctl->drain));
             mbar_wait(smem_u32(&ctl->drain), 0, abort_flag, a.status, 206);
         }
     } else {
@@ -329,79 +385,97 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             m = (mx == -INFINITY) ? 0.f : mx * a.scale_log2;
         }
 
-        float l0 = 0.f, l1 = 0.f, l2 = 0.f, l3 = 0.f;
+        float2 lsum[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
         const int* rl = a.refine + (size_t)th_idx * a.rw;
         const float* lc = a.log_counts + (size_t)h * a.nb4;
         const int* bits = a.skip_bits + ((size_t)h * a.nq + qb) * a.nw;
         const bool want_mass = !FALLBACK && a.mass != nullptr;
+        const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
 
+        // block ids of the exact iteration that comes next, loaded one iteration ahead
+        int nba = n > 0 ? list[0] : 0, nbb = n64 > 1 ? list[1] : nba;
+        // thread 0 stores the masses of an iteration at the start of the next one: by then the other warps' partial sums
+        // have long arrived, so the store never holds back the warp that the other three wait for
+        int pend_a = -1, pend_b = -1, pend_buf = 0;
+        auto flush_mass = [&]() {
+            if (tid == 0 && pend_a >= 0) {
+                ok = mbar_wait(smem_u32(&ctl->massbar), uM & 1, abort_flag, a.status, 304);
+                ++uM;
+                if (ok) {
+                    const float* mp = ctl->mass_part[pend_buf][0];
+                    float* mrow = a.mass + ((size_t)h * a.nq + qb) * a.nb;
+                    mrow[pend_a] = ((mp[0] + mp[1]) + mp[2]) + mp[3];
+                    if (pend_b >= 0) mrow[pend_b] = ((mp[4] + mp[5]) + mp[6]) + mp[7];
+                }
+                pend_a = -1;
+            }
+        };
         for (int i = 0; i < nt && ok; ++i) {
             const bool exact = i < n, pooled = !exact && i < n + nvirt;
-            int ba = 0, bb = 0;
-            bool has_b = true;
-            if (exact) {
-                ba = list[2 * i];
-                has_b = 2 * i + 1 < n64;
-                bb = has_b ? list[2 * i + 1] : ba;
+            const int ba = nba, bb = nbb;
+            const bool has_b = 2 * i + 1 < n64 || !exact;
+            if (i + 1 < n) {
+                nba = list[2 * i + 2];
+                nbb = 2 * i + 3 < n64 ? list[2 * i + 3] : nba;
             }
+            flush_mass();
             float part[2];
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
+                if (tid == 0) trace_put(a.trace, 0, i, x, 0, t_start);
                 ok = ok && mbar_wait(smem_u32(&ctl->sfull[x]), uS[x] & 1, abort_flag, a.status, 302);
                 if (!ok) break;
+                if (tid == 0) trace_put(a.trace, 0, i, x, 1, t_start);
                 ++uS[x];
                 tc_fence_after();
                 tmem_ld32(lane_base + x * BK, &s[0]);
                 tmem_ld32(lane_base + x * BK + 32, &s[32]);
                 tmem_wait_ld();
-                float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+                if (tid == 0) trace_put(a.trace, 0, i, x, 2, t_start);
+                float2 acc = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
                 uint32_t pk[32];
                 if (exact) {
                     const int blk = x == 0 ? ba : bb;
                     int lim = (blk == a.nb - 1) ? a.tail_valid : BK;
                     if (x == 1 && !has_b) lim = 0;
-                    const float noff = -m;
+                    const float2 off2 = make_float2(-m, -m);
                     if (lim == BK) {
 #pragma unroll
-                        for (int c = 0; c < 64; c += 4) {
-                            const float p0 = ex2_approx(fmaf(__uint_as_float(s[c]), a.scale_log2, noff));
-                            const float p1 = ex2_approx(fmaf(__uint_as_float(s[c + 1]), a.scale_log2, noff));
-                            const float p2 = ex2_approx(fmaf(__uint_as_float(s[c + 2]), a.scale_log2, noff));
-                            const float p3 = ex2_approx(fmaf(__uint_as_float(s[c + 3]), a.scale_log2, noff));
-                            a0 += p0; a1 += p1; a2 += p2; a3 += p3;
-                            pk[c / 2] = pack_bf16x2(p0, p1);
-                            pk[c / 2 + 1] = pack_bf16x2(p2, p3);
+                        for (int j = 0; j < 32; ++j) {
+                            const float2 xv = __ffma2_rn(make_float2(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1])), sc2, off2);
+                            const float2 p = emulate_pair(j) ? exp2_pair_fma(xv) : exp2_pair_mufu(xv);
+                            if (j & 1) acc1 = __fadd2_rn(acc1, p); else acc = __fadd2_rn(acc, p);
+                            pk[j] = pack_bf16x2(p.x, p.y);
                         }
                     } else {
 #pragma unroll
-                        for (int c = 0; c < 64; c += 2) {
-                            float p0 = ex2_approx(fmaf(__uint_as_float(s[c]), a.scale_log2, noff));
-                            float p1 = ex2_approx(fmaf(__uint_as_float(s[c + 1]), a.scale_log2, noff));
-                            p0 = c < lim ? p0 : 0.f;
-                            p1 = c + 1 < lim ? p1 : 0.f;
-                            a0 += p0; a1 += p1;
-                            pk[c / 2] = pack_bf16x2(p0, p1);
+                        for (int j = 0; j < 32; ++j) {
+                            const float2 xv = __ffma2_rn(make_float2(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1])), sc2, off2);
+                            float2 p = exp2_pair_mufu(xv);
+                            p.x = 2 * j < lim ? p.x : 0.f;
+                            p.y = 2 * j + 1 < lim ? p.y : 0.f;
+                            acc = __fadd2_rn(acc, p);
+                            pk[j] = pack_bf16x2(p.x, p.y);
                         }
                     }
                 } else if (pooled) {
                     // block-mean columns: column c of this half is block 128 cv + 64 x + c; a set bit masks it
                     const int cv = i - n;
                     const uint32_t w0 = (uint32_t)bits[4 * cv + 2 * x], w1 = (uint32_t)bits[4 * cv + 2 * x + 1];
-                    const float noff = -m + 6.0f;                  // log2(64): a mean stands for its block's tokens
+                    const float2 off2 = make_float2(-m + 6.0f, -m + 6.0f);   // log2(64): a mean stands for its block's tokens
                     const int last_c = (a.nb - 1) - (128 * cv + 64 * x);   // column of the (maybe shorter) last block
                     const float fix = a.tail_log2 - 6.0f;
 #pragma unroll
-                    for (int c = 0; c < 64; c += 2) {
-                        float x0 = fmaf(__uint_as_float(s[c]), a.scale_log2, noff);
-                        float x1 = fmaf(__uint_as_float(s[c + 1]), a.scale_log2, noff);
-                        if (c == last_c) x0 += fix;
-                        if (c + 1 == last_c) x1 += fix;
-                        float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
-                        const uint32_t w = c < 32 ? w0 : w1;
-                        p0 = ((w >> (c & 31)) & 1u) ? 0.f : p0;
-                        p1 = ((w >> ((c + 1) & 31)) & 1u) ? 0.f : p1;
-                        a0 += p0; a1 += p1;
-                        pk[c / 2] = pack_bf16x2(p0, p1);
+                    for (int j = 0; j < 32; ++j) {
+                        float2 xv = __ffma2_rn(make_float2(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1])), sc2, off2);
+                        if (2 * j == last_c) xv.x += fix;
+                        if (2 * j + 1 == last_c) xv.y += fix;
+                        float2 p = exp2_pair_mufu(xv);
+                        const uint32_t w = j < 16 ? w0 : w1;
+                        p.x = ((w >> ((2 * j) & 31)) & 1u) ? 0.f : p.x;
+                        p.y = ((w >> ((2 * j + 1) & 31)) & 1u) ? 0.f : p.y;
+                        acc = __fadd2_rn(acc, p);
+                        pk[j] = pack_bf16x2(p.x, p.y);
                     }
                 } else {
                     // representatives: columns 4e .. 4e+3 of this half belong to list entry 32 cr + 16 x + e
@@ -415,22 +489,27 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         for (int j = 0; j < 4; ++j) {
                             const float4 b4 = __ldg(reinterpret_cast<const float4*>(lc + 4 * bl[j]));
                             const int c = 16 * e4 + 4 * j;
-                            const float p0 = ex2_approx(fmaf(__uint_as_float(s[c]), a.scale_log2, b4.x - m));
-                            const float p1 = ex2_approx(fmaf(__uint_as_float(s[c + 1]), a.scale_log2, b4.y - m));
-                            const float p2 = ex2_approx(fmaf(__uint_as_float(s[c + 2]), a.scale_log2, b4.z - m));
-                            const float p3 = ex2_approx(fmaf(__uint_as_float(s[c + 3]), a.scale_log2, b4.w - m));
-                            a0 += p0; a1 += p1; a2 += p2; a3 += p3;
-                            pk[c / 2] = pack_bf16x2(p0, p1);
-                            pk[c / 2 + 1] = pack_bf16x2(p2, p3);
+                            const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2,
+                                                         make_float2(b4.x - m, b4.y - m));
+                            const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), sc2,
+                                                         make_float2(b4.z - m, b4.w - m));
+                            const float2 p0 = exp2_pair_mufu(x0), p1 = exp2_pair_mufu(x1);
+                            acc = __fadd2_rn(acc, p0);
+                            acc1 = __fadd2_rn(acc1, p1);
+                            pk[c / 2] = pack_bf16x2(p0.x, p0.y);
+                            pk[c / 2 + 1] = pack_bf16x2(p1.x, p1.y);
                         }
                     }
                 }
+                if (tid == 0) trace_put(a.trace, 0, i, x, 3, t_start);
                 tmem_st32(lane_base + x * BK, pk);
                 tmem_wait_st();
                 tc_fence_before();
                 mbar_arrive(smem_u32(&ctl->pfull[x]));
-                part[x] = (a0 + a1) + (a2 + a3);
-                if (x == 0) { l0 += a0 + a2; l1 += a1 + a3; } else { l2 += a0 + a2; l3 += a1 + a3; }
+                if (tid == 0) trace_put(a.trace, 0, i, x, 4, t_start);
+                acc = __fadd2_rn(acc, acc1);
+                part[x] = acc.x + acc.y;
+                lsum[x] = __fadd2_rn(lsum[x], acc);
             }
             if (!ok) break;
             if (want_mass && exact) {
@@ -444,27 +523,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                 }
                 // The partial sums are double-buffered over iterations: a warp can write those of iteration i + 2
                 // only after S(i + 2) exists, which needs thread 0's pfull arrivals of iteration i + 1, made after
-                // its sum of iteration i.
+                // it has stored the masses of iteration i.
                 if (lane == 0) {
                     ctl->mass_part[i & 1][0][warp] = pa;
                     ctl->mass_part[i & 1][1][warp] = pb;
                     mbar_arrive(smem_u32(&ctl->massbar));
                 }
-                if (tid == 0) {
-                    ok = mbar_wait(smem_u32(&ctl->massbar), uM & 1, abort_flag, a.status, 304);
-                    if (ok) {
-                        const float* mp = ctl->mass_part[i & 1][0];
-                        float* mrow = a.mass + ((size_t)h * a.nq + qb) * a.nb;
-                        mrow[ba] = ((mp[0] + mp[1]) + mp[2]) + mp[3];
-                        if (has_b) mrow[bb] = ((mp[4] + mp[5]) + mp[6]) + mp[7];
-                    }
-                }
-                ++uM;
+                pend_a = ba;
+                pend_b = has_b ? bb : -1;
+                pend_buf = i & 1;
             }
         }
+        if (ok) flush_mass();
 
         // ---- epilogue
-        const float l = (l0 + l1) + (l2 + l3);
+        const float l = (lsum[0].x + lsum[0].y) + (lsum[1].x + lsum[1].y);
         const float lg = log2f(l);
         const bool valid = row < a.L;
         if (nt > 0) ok = ok && mbar_wait(smem_u32(&ctl->ofull), 0, abort_flag, a.status, 303);
@@ -517,9 +590,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
             for (uint32_t t = 0; t < (1u << 20) && !mbar_try_wait(bar, parity); ++t) {}
         };
         settle(smem_u32(&ctl->qfull), 0);
-        for (int x = 0; x < 2; ++x) {
-            if (uK[x]) settle(smem_u32(&ctl->kfull[x]), (uK[x] - 1) & 1);
-            if (uV[x]) settle(smem_u32(&ctl->vfull[x]), (uV[x] - 1) & 1);
+        for (uint32_t back = 1; back <= NSLOT && back <= pseq; ++back) {
+            const uint32_t sq = pseq - back;
+            settle(smem_u32(&ctl->full[sq % NSLOT]), (sq / NSLOT) & 1);
         }
     }
     __syncwarp();
@@ -541,6 +614,8 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int H, int box_ro
     return encode_tensor_map(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
                              CU_TENSOR_MAP_SWIZZLE_128B);
 }
+
+static uint32_t* g_trace = nullptr;
 
 struct AttnCall {
     const void *q, *k, *v, *k_mean, *v_mean;
@@ -586,6 +661,7 @@ static void fill_common(AttnArgs& a, int L, int H, float threshold) {
     a.tail_valid = L - (a.nb - 1) * BK;
     a.tail_log2 = log2f((float)a.tail_valid);
     a.status = device_status_ptr();
+    a.trace = g_trace;
 }
 
 }  // namespace es
@@ -645,3 +721,11 @@ extern "C" int es_exact_fallback(const void* q, const void* k, const void* v, vo
     c.a.nvirt = 0; c.a.nref = 0;
     return launch_attention(c, true, (cudaStream_t)stream);
 }
+
+// Debugging aid: when `buffer` (device memory, es_debug_trace_words() 32-bit words, zeroed by the caller) is not NULL,
+// the attention kernels launched afterwards record clock stamps of their first CTAs' pipeline stages into it.
+extern "C" int es_debug_set_trace(void* buffer) {
+    es::g_trace = static_cast<uint32_t*>(buffer);
+    return 0;
+}
+extern "C" int es_debug_trace_words(void) { return es::TRACE_CTAS * 2 * es::TRACE_ITERS * 2 * 8; }
