@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "_lib", "libechosparse_sm100.so")
+# ECHOSPARSE_SM100_LIB selects another build of the same library (for example one compiled with -DES_TRACE).
+LIB_PATH = os.environ.get("ECHOSPARSE_SM100_LIB") or os.path.join(_HERE, "_lib", "libechosparse_sm100.so")
 
 _P = ctypes.c_void_p
 _I = ctypes.c_int32
