@@ -101,6 +101,19 @@ int es_reps_gram_splits(int32_t L);
 int es_reps_metric(const void* q, float* gram_parts, float* gram, void* metric, void* probes, int32_t L, int32_t H,
                    void* stream);
 
+/* The same as es_reps_metric for callers that cannot provide scratch memory (no counterpart in the reference).
+ * Some hosts of this library may not allocate device memory at the point where they call it: a plugin running inside
+ * another framework's memory pool, a caller inside a region where allocation is forbidden or would synchronise. This
+ * entry point takes no scratch pointer and calls no allocator: the partial Gram sums go to a 16 MiB array that is part
+ * of the library image on every GPU that loads it. Limits and rules:
+ *   - H <= es_reps_metric_static_max_heads() (256); more heads are rejected with an error;
+ *   - the first call on a device looks up the array's device address; make that call outside any stream capture;
+ *   - all calls share the one array: calls that may overlap on the GPU (different streams) race and must be serialised
+ *     by the caller. Nothing in the array has to start at zero: every call overwrites what it reads.
+ * Results match es_reps_metric within rounding (the rows are split into fewer partial sums when H is large). */
+int es_reps_metric_static(const void* q, float* gram, void* metric, void* probes, int32_t L, int32_t H, void* stream);
+int es_reps_metric_static_max_heads(void);
+
 /* Representatives of every kv block. Replaces the k-means launch of echosparse/kernels/representatives.py:147 `build`.
  * k_rep, v_rep (H, (nb+1)*4, 128) bf16 and log_counts (H, (nb+1)*4) fp32; block nb of the tables is not written.
  * k_mean, v_mean (nb, H, 128) bf16 are also written when both are given (NULL, NULL otherwise). */

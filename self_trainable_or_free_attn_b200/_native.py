@@ -34,6 +34,8 @@ SIGNATURES = {
     "es_reps_gram_splits": [_I],
     "es_reps_metric": [_P, _P, _P, _P, _P, _I, _I, _P],
     "es_reps_kmeans": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    "es_reps_metric_static": [_P, _P, _P, _P, _I, _I, _P],
+    "es_reps_metric_static_max_heads": [],
     "es_debug_set_trace": [_P],
     "es_debug_trace_words": [],
 }

@@ -394,3 +394,59 @@ extern "C" int es_reps_kmeans(const void* k, const void* v, const void* metric, 
     ES_CHECK_LAUNCH("kmeans");
     return 0;
 }
+
+// ------------------------------------------------------------------------------------------------ no-allocation variant
+// Scratch for es_reps_metric_static: room for ES_STATIC_GRAM_PARTS partial Gram matrices (128 x 128 floats each), held by
+// every GPU that loads this library from load to exit.
+#define ES_STATIC_GRAM_PARTS 256
+static __device__ __align__(256) float g_static_gram_parts[ES_STATIC_GRAM_PARTS * HD * HD];
+
+// Device address of the scratch array on the current device. In host code the array's name is only a handle for the
+// runtime, not an address a kernel could use, so the address is asked for once per device (with that device current).
+static float* static_gram_parts() {
+    static float* ptrs[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_static_gram_parts) != cudaSuccess) return nullptr;
+        ptrs[dev] = static_cast<float*>(p);
+    }
+    return ptrs[dev];
+}
+
+extern "C" int es_reps_metric_static_max_heads(void) { return ES_STATIC_GRAM_PARTS; }
+
+extern "C" int es_reps_metric_static(const void* q, float* gram, void* metric, void* probes, int32_t L, int32_t H,
+                                     void* stream) {
+    if (!q || !metric || !probes) return set_error(-1, "es_reps_metric_static: null pointer");
+    if (L <= 0 || H <= 0) return set_error(-1, "es_reps_metric_static: L and H must be positive");
+    if ((uintptr_t)q & 15) return set_error(-1, "es_reps_metric_static: q must be 16-byte aligned");
+    if (H > ES_STATIC_GRAM_PARTS)
+        return set_error(-1, "es_reps_metric_static: more than 256 heads do not fit the built-in scratch; use es_reps_metric");
+    float* parts = static_gram_parts();
+    if (!parts) return set_error(-2, "es_reps_metric_static: the address of the built-in scratch is not available");
+    // as many row splits as the scratch holds for this head count (at most the usual number)
+    int nsplit = ES_STATIC_GRAM_PARTS / H;
+    const int usual = es_reps_gram_splits(L);
+    if (nsplit > usual) nsplit = usual;
+    const int rps = (((L + nsplit - 1) / nsplit + 63) / 64) * 64;
+    nsplit = (L + rps - 1) / rps;
+    const int nb = (L + 63) / 64;
+    cudaStream_t st = (cudaStream_t)stream;
+    gram_kernel<<<dim3(H, nsplit), 256, 0, st>>>((const __nv_bfloat16*)q, parts, L, H, rps, nsplit);
+    ES_CHECK_LAUNCH("gram");
+    const int smem = (2 * HD * 129 + HD) * (int)sizeof(float);
+    static bool attr = false;
+    if (!attr) {
+        cudaError_t e = cudaFuncSetAttribute(metric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
+        attr = true;
+    }
+    const float scale = 1.0f / sqrtf((float)HD);
+    metric_kernel<<<H, 256, smem, st>>>(parts, (__nv_bfloat16*)metric, gram, nsplit, scale * scale / (float)L);
+    ES_CHECK_LAUNCH("metric");
+    probe_kernel<<<dim3(NP, H), HD, 0, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)probes, L, H, nb, scale);
+    ES_CHECK_LAUNCH("probes");
+    return 0;
+}
