@@ -16,13 +16,15 @@
 //
 // Pipeline. An iteration covers 128 columns (two 64-token blocks, 128 block means, or 32 refine entries x 4).
 //   warps 0-7  softmax: warp w owns rows 32 (w % 4) .. +31 of the tile and columns 64 (w / 4) .. +63 of the iteration
-//   warp 8     issues the tcgen05 MMAs (one elected lane), warp 9 issues the TMA loads / cp.async gathers
+//   warp 8     issues the tcgen05 MMAs (one elected lane); warps 9 and 10 issue the TMA loads / cp.async gathers of the K
+//              and of the V tiles (control code is one dependent chain per tile: two warps halve its length)
 // Tensor memory (512 columns): S of even iterations [0,128), S of odd iterations [128,256), O [256,384), Q [384,448).
 // Q sits in tensor memory as the A operand of QK^T, so the only shared-memory traffic of the MMAs is K and V: with Q in
 // shared memory a 128 x 64 x 16 MMA reads 6 KB in the 32 clocks it computes, more than the 128 B/clock an SM delivers.
 // P (bf16 pairs) is written over the S columns it came from and is the A operand of PV. Two S buffers let QK of
 // iteration i + 1 run while the softmax warps work on iteration i; PV(i) and QK(i + 2) follow as soon as P(i) is stored.
-// K and V tiles (32 KB each) travel through a ring of 7 shared-memory slots, about three iterations ahead of the MMAs.
+// K and V tiles (32 KB each, [d half][128 rows][128 B], four 8 KB TMA boxes) travel through a ring of 7 shared-memory slots,
+// about three iterations ahead of the MMAs.
 #include "es_ptx.cuh"
 #include "es_api_internal.h"
 
@@ -32,15 +34,15 @@ constexpr int BM = 128;       // query rows per tile
 constexpr int BK = 64;        // tokens per kv block
 constexpr int HD = 128;       // head dim
 constexpr int NSOFT = 256;    // softmax threads
-constexpr int NTHREADS = NSOFT + 64;
-constexpr int MMA_WARP = NSOFT / 32, LOAD_WARP = MMA_WARP + 1;
+constexpr int NTHREADS = NSOFT + 96;
+constexpr int MMA_WARP = NSOFT / 32, LOADK_WARP = MMA_WARP + 1, LOADV_WARP = MMA_WARP + 2;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t O_COL = 256, Q_COL = 384;
 constexpr int NSLOT = 7;      // K / V tiles in flight
 
 constexpr uint32_t TILE_BYTES = 128 * HD * 2;    // 32 KB: [d half][128 rows][64 d], 128B-swizzled
 constexpr uint32_t HALF_BYTES = TILE_BYTES / 2;  // one d half: 128 rows x 128 B
-constexpr uint32_t BLK_BYTES = BK * 128;         // 64 rows of one d half
+constexpr uint32_t BLK_BYTES = BK * 128;         // 64 rows of one d half: one TMA box
 constexpr uint32_t SMEM_RING = 0;
 constexpr uint32_t SMEM_CTL = SMEM_RING + NSLOT * TILE_BYTES;
 constexpr uint32_t SMEM_ALLOC = SMEM_CTL + 3072;   // 232,448 B: all of an SM's shared memory
@@ -51,6 +53,7 @@ struct Ctl {
     uint64_t sfull[2], pfull[2];
     uint64_t ofull, drain;
     uint64_t massbar, flagbar, lbar;   // softmax warps -> the thread(s) that combine their partial results
+    uint64_t sweepbar;                 // K load warp -> V load warp: the fallback sweep's tiles have all been issued
     uint32_t tmem_base;
     int abort;
     int flag_part[4];
@@ -138,8 +141,10 @@ __device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
     return p;
 }
 // Pair j (columns 2j, 2j+1) of a thread's 64 columns goes to the FMA pipe when bit (j & 7) of ES_EMU_PATTERN is set.
+// Measured on B200 with this kernel: 0x00 (all MUFU) 1.549 ms, 0x11 1.561 ms, 0x55 1.660 ms (Wan-1.3B shape), so the
+// default keeps every exponential on MUFU; the FMA path stays available for parts with a different balance.
 #ifndef ES_EMU_PATTERN
-#define ES_EMU_PATTERN 0x11
+#define ES_EMU_PATTERN 0x0
 #endif
 __device__ __forceinline__ constexpr bool emulate_pair(int j) { return (ES_EMU_PATTERN >> (j & 7)) & 1; }
 
@@ -155,6 +160,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     if (FALLBACK) {
         if (a.flags[th_idx] == 0) return;          // uniform over the CTA, before anything is allocated
     }
+    // a wait has given up earlier (the status word is set until the host reads it): do not start more work
+    if (*reinterpret_cast<volatile int*>(a.status) != 0) return;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
@@ -178,6 +185,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         mbar_init(smem_u32(&ctl->massbar), 8);
         mbar_init(smem_u32(&ctl->flagbar), 4);
         mbar_init(smem_u32(&ctl->lbar), NSOFT);
+        mbar_init(smem_u32(&ctl->sweepbar), 1);
         ctl->abort = (base & 1023u) ? 1 : 0;
         mbar_fence_init();
         fence_proxy_async_smem();
@@ -201,72 +209,85 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     // K and V tiles travel through one ring of NSLOT slots in the order the MMA warp consumes them:
     //   [fallback sweep: K(0) K(1) ... K(n-1)]  K(0) K(1)  { V(i) K(i+2) } for i = 0 .. nt-1
     // tile number `seq` lives in slot seq % NSLOT; its barriers are in phase (seq / NSLOT) & 1.
-    uint32_t pseq = 0;                                // producer: tiles issued (used again at teardown)
+    uint32_t pseq = 0;                                // load warps: one past the last tile issued (used again at teardown)
 
-    if (warp == LOAD_WARP) {
-        // ------------------------------------------------------------ loads (all lanes walk the sequence together)
+    if (warp == LOADK_WARP || warp == LOADV_WARP) {
+        // ------------------------------------------------------------ loads: one warp walks the K tiles, one the V tiles
+        const bool is_v = warp == LOADV_WARP;
         bool ok = true;
-        if (lane == 0) { tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); }
-        const __nv_bfloat16* krep = a.k_rep + (size_t)h * a.nb4 * HD;
-        const __nv_bfloat16* vrep = a.v_rep + (size_t)h * a.nb4 * HD;
+        const CUtensorMap* map_x = is_v ? &tmV : &tmK;       // exact blocks
+        const CUtensorMap* map_m = is_v ? &tmVm : &tmKm;     // block means
+        if (lane == 0) { tma_prefetch_desc(map_x); tma_prefetch_desc(map_m); }
+        const __nv_bfloat16* rep = (is_v ? a.v_rep : a.k_rep) + (size_t)h * a.nb4 * HD;
         const int* rl = a.refine + (size_t)th_idx * a.rw;
-        // Block ids come from two 32-entry windows of the list held across the lanes (one for the K sequence, one for
-        // the V sequence, which runs two iterations behind): one coalesced load per 16 iterations instead of two
-        // dependent global loads in front of every tile.
-        int win[2] = {0, 0}, wbase[2] = {-1, -1};
-        auto block_of = [&](int which, int e) -> int {
-            const int b0 = e & ~31;
-            if (b0 != wbase[which]) {
-                wbase[which] = b0;
-                win[which] = (b0 + lane < n64) ? list[b0 + lane] : 0;
-            }
-            return __shfl_sync(0xffffffffu, win[which], e & 31);
-        };
-        // the K (is_v = false) or V tile of iteration i. The code of this warp is one dependent chain per tile, so it is
-        // kept short: ring position by counters, the four TMA boxes of a tile issued by four lanes at once.
-        uint32_t pslot = 0, ppar = 1;
         const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
         const uint32_t box_off = (uint32_t)(lane >> 1) * HALF_BYTES + (uint32_t)(lane & 1) * BLK_BYTES;   // lanes 0..3
         const int box_x = (lane >> 1) * 64;
-        auto put = [&](int i, bool is_v, int ti = TRACE_ITERS) {
+        // block ids: a 32-entry window of the list held across the lanes, one coalesced load per 16 iterations
+        int win = 0, wbase = -1;
+        // tile number `seq` of the ring: K or V tile of iteration i (i < 0: K tile -i-1 of the fallback sweep)
+        auto put = [&](uint32_t seq, int i) {
             if (!ok) return;
-            if (lane == 0 && is_v) trace_put(a.trace, 0, ti, 7, t_start);
-            int ra = 0, rb = 0;
+            int ra = 0, rb = 64;
+            const CUtensorMap* m = map_m;
             if (i < n) {
-                ra = block_of(is_v, 2 * i) * BK;
-                rb = (2 * i + 1 < n64) ? block_of(is_v, 2 * i + 1) * BK : ra;   // odd list: block a again, masked in the softmax
-            } else if (i < n + nvirt) {
-                ra = (i - n) * 128;                                            // rows of the block-mean tables
+                const int e = 2 * i;
+                if ((e & ~31) != wbase) {
+                    wbase = e & ~31;
+                    win = (wbase + lane < n64) ? list[wbase + lane] : 0;
+                }
+                ra = __shfl_sync(0xffffffffu, win, e & 31) * BK;
+                rb = __shfl_sync(0xffffffffu, win, (e + 1) & 31) * BK;
+                if (e + 1 >= n64) rb = ra;                     // odd list: block a again, masked in the softmax
+                m = map_x;
+            } else {
+                ra = (i - n) * 128;                            // rows of the block-mean tables
                 rb = ra + 64;
             }
-            if (lane == 0) ok = mbar_wait(empty0 + 8 * pslot, ppar, abort_flag, a.status, 101);
+            const uint32_t slot = seq % NSLOT, par = ((seq / NSLOT) & 1) ^ 1;
+            if (lane == 0) ok = mbar_wait(empty0 + 8 * slot, par, abort_flag, a.status, 101);
             ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;     // the other lanes sleep at the shuffle instead of polling
             if (!ok) return;
-            const uint32_t dst = sRing + pslot * TILE_BYTES, bar = full0 + 8 * pslot;
+            const uint32_t dst = sRing + slot * TILE_BYTES, bar = full0 + 8 * slot;
+#ifdef ES_EXPERIMENT_NOLOAD
+            if (seq >= NSLOT) {                 // timing experiment only: tiles after the first ring round are not loaded
+                if (lane == 0) mbar_arrive(bar);
+            } else
+#endif
             if (i < n + nvirt) {
                 if (lane == 0) mbar_arrive_expect_tx(bar, TILE_BYTES);
                 __syncwarp();
-                if (lane < 4) {
-                    const CUtensorMap* m = i < n ? (is_v ? &tmV : &tmK) : (is_v ? &tmVm : &tmKm);
-                    tma_load_3d(dst + box_off, m, bar, box_x, (lane & 1) ? rb : ra, h);
-                }
+                if (lane < 4) tma_load_3d(dst + box_off, m, bar, box_x, (lane & 1) ? rb : ra, h);
             } else {
                 // refine iteration: list entry 32 c + e fills columns 4e .. 4e+3 of the 128-column tile
                 const int my = rl[32 * (i - n - nvirt) + lane];
-                gather_tile(dst, is_v ? vrep : krep, my, lane, bar);
+                gather_tile(dst, rep, my, lane, bar);
             }
-            if (lane == 0) trace_put(a.trace, 0, ti, is_v ? 5 : 6, t_start);
-            if (++pslot == NSLOT) { pslot = 0; ppar ^= 1; }
-            ++pseq;
+            pseq = seq + 1;
         };
+        uint32_t base = 0;
         if (FALLBACK) {
-            for (int i = 0; i < n; ++i) put(i, false);
+            // The sweep's K tiles come first in the ring. A wait on a slot's `empty` barrier can only tell two consecutive
+            // rounds apart (one parity bit), so the V warp must not start polling while the ring is still rounds behind
+            // its first tile: it starts once the K warp has issued the last sweep tile.
+            if (!is_v) {
+                for (int i = 0; i < n; ++i) put((uint32_t)i, i);
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->sweepbar));
+            } else {
+                if (lane == 0) ok = mbar_wait(smem_u32(&ctl->sweepbar), 0, abort_flag, a.status, 102);
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+            }
+            base = (uint32_t)n;
+            wbase = -1;
         }
-        if (nt > 0) put(0, false);
-        if (nt > 1) put(1, false);
-        for (int i = 0; i < nt; ++i) {
-            put(i, true, i);
-            if (i + 2 < nt) put(i + 2, false, i);
+        if (!is_v) {
+            // K(0), K(1), then K(i + 2) after every V(i)
+            if (nt > 0) put(base, 0);
+            if (nt > 1) put(base + 1, 1);
+            for (int i = 2; i < nt; ++i) put(base + 2 * i - 1, i);
+        } else {
+            // V(i) comes after the K tiles 0 .. min(i + 2, nt) - 1 and the V tiles before it
+            for (int i = 0; i < nt; ++i) put(base + (uint32_t)(min(i + 2, nt) + i), i);
         }
     } else if (warp == MMA_WARP) {
         // ------------------------------------------------------------ MMAs: the warp runs uniformly, one elected lane issues
@@ -333,8 +354,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 const uint32_t vb_lo = v_lo0 + ((sRing + slot * TILE_BYTES) >> 4);
 #pragma unroll
                 for (int ks = 0; ks < 8; ++ks)
-                    umma_ts_lohi(tmem + O_COL, p + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8), vb_lo + (uint32_t)((ks * 2048) >> 4),
-                                 v_hi, IDESC_PV, (i > 0 || ks > 0) ? 1u : 0u);
+                    umma_ts_lohi(tmem + O_COL, p + (ks < 4 ? ks * 8 : 64 + (ks - 4) * 8),
+                                 vb_lo + (uint32_t)((ks * 2048) >> 4), v_hi, IDESC_PV,
+                                 (i > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(empty0 + 8 * slot);
                 if (i + 1 == nt) umma_commit(smem_u32(&ctl->ofull));
             }
@@ -596,12 +618,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 
     // ---------------------------------------------------------------- teardown
     __syncwarp();
-    if (warp == LOAD_WARP && lane == 0 && *abort_flag) {
-        // a wait gave up somewhere: let the loads already issued land before the CTA's shared memory goes away
+    if ((warp == LOADK_WARP || warp == LOADV_WARP) && lane == 0 && *abort_flag) {
+        // a wait gave up somewhere: let the loads this warp issued land before the CTA's shared memory goes away
         auto settle = [](uint32_t bar, uint32_t parity) {
             for (uint32_t t = 0; t < (1u << 20) && !mbar_try_wait(bar, parity); ++t) {}
         };
-        for (uint32_t back = 1; back <= NSLOT && back <= pseq; ++back) {
+        for (uint32_t back = 1; back <= 2 * NSLOT && back <= pseq; ++back) {
             const uint32_t sq = pseq - back;
             settle(smem_u32(&ctl->full[sq % NSLOT]), (sq / NSLOT) & 1);
         }

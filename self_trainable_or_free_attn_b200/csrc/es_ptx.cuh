@@ -46,9 +46,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Wait limit of every barrier wait in this library: far above any legitimate wait (a CTA lives for well under a
 // second), short enough that a stuck pipeline returns quickly.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+constexpr uint64_t kWaitLimitNs = 500000000ull;
 
-// Bounded wait. `abort_flag` (shared memory) is set by the first wait that gives up; later waits return at once.
+// Bounded wait. `abort_flag` (shared memory) is set by the first wait of the CTA that gives up; later waits return at
+// once. The device status word is checked too, so once one CTA has given up the others stop waiting as well and the
+// kernel ends quickly instead of after one time limit per CTA.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -58,6 +60,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         if (mbar_try_wait(bar, parity)) return true;
         if ((++polls & 63u) == 0) {
             if (*abort_flag) return false;
+            if (*reinterpret_cast<volatile int*>(status) != 0) {
+                *abort_flag = 1;
+                return false;
+            }
             if (global_timer_ns() - t0 > kWaitLimitNs) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code);
@@ -101,6 +107,13 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* m, 
     asm volatile(
         "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* m, uint32_t bar, int x, int y, int z, int w) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(x), "r"(y), "r"(z), "r"(w)
         : "memory");
 }
 

@@ -147,12 +147,27 @@ probe_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ pr
 }
 
 // ------------------------------------------------------------------------------------------------ k-means
-constexpr int KS = 130;           // bf16 row stride of the K tile (65 words: rows land in distinct banks)
-constexpr int XS = 129;           // float row stride of X and of the centroids
+// One CTA (8 warps) per (kv block, head). The two contractions (X = K M, probe scores = P K^T) run on the tensor cores
+// (mma.sync m16n8k16, bf16 products with float32 sums, the arithmetic of the reference's tl.dot on bf16 inputs); the
+// Lloyd iterations work on X in shared memory in float32 with all 256 threads busy in every phase.
+constexpr int KS = 136;           // bf16 row stride of the K tile: 272 B, so the 8 rows of an ldmatrix hit distinct banks
+constexpr int XS = 132;           // float row stride of X and of the centroids
 constexpr int PS = 65;            // float row stride of the probe scores
-constexpr int KM_SMEM = 64 * KS * 2 + 64 * XS * 4 + 64 * PS * 4 + 4 * XS * 4 + 64 * 4 * 2 + 64;
+constexpr int KM_SMEM = 64 * KS * 2 + 64 * XS * 4 + 64 * PS * 4 + 4 * XS * 4 + 4 * 64 * 4 + 64 * 4 + 64 * 4;
 
-__global__ void __launch_bounds__(256)
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+__global__ void __launch_bounds__(256, 3)
 kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
               const __nv_bfloat16* __restrict__ metric, const __nv_bfloat16* __restrict__ probes,
               __nv_bfloat16* __restrict__ k4, __nv_bfloat16* __restrict__ v4, float* __restrict__ c4,
@@ -162,12 +177,14 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     float* sX = reinterpret_cast<float*>(raw + 64 * KS * 2);                        // [64][XS]
     float* sP = sX + 64 * XS;                                                       // [64 probes][PS]
     float* cen = sP + 64 * PS;                                                      // [4][XS]
-    float* w = cen + 4 * XS;                                                        // [64]
+    float* wpart = cen + 4 * XS;                                                    // [4][64]
+    float* w = wpart + 4 * 64;                                                      // [64]
     int* lab = reinterpret_cast<int*>(w + 64);                                      // [64]
-    __shared__ float cw[4];
+    __shared__ float cw[4], cnorm[4];
     __shared__ int s_changed;
     __shared__ float s_cnt[4];
-    const int j = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int j = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, tg = lane & 3;
     const int nvalid = min(L - j * 64, 64);
 
     // K tile (rows past L are zero)
@@ -175,116 +192,156 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
         const int r = e >> 4, c16 = e & 15;
         uint4 x = make_uint4(0, 0, 0, 0);
         if (r < nvalid) x = *reinterpret_cast<const uint4*>(k + ((size_t)(j * 64 + r) * H + h) * HD + c16 * 8);
-        uint32_t* d = reinterpret_cast<uint32_t*>(sK + r * KS + c16 * 8);
-        d[0] = x.x; d[1] = x.y; d[2] = x.z; d[3] = x.w;
+        *reinterpret_cast<uint4*>(sK + r * KS + c16 * 8) = x;
     }
     __syncthreads();
 
-    // X = K M (bf16 products, fp32 sums): thread -> rows 4 ty .., columns 8 tx ..
+    const int mt = warp & 3, nh = warp >> 2;
+    // A fragments of this warp's 16 tokens (rows 16 mt ..), all 8 k-steps: shared by both contractions below? No: the
+    // probe scores use K as the B operand. Only X uses these.
     {
-        const int ty = tid >> 4, tx = tid & 15;
-        float acc[4][8];
+        // X = K M: rows 16 mt .. +15, columns 64 nh .. +63
+        float acc[8][4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
+        for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-            for (int b = 0; b < 8; ++b) acc[a][b] = 0.f;
-        const __nv_bfloat16* mh = metric + (size_t)h * HD * HD + tx * 8;
-#pragma unroll 4
-        for (int kk = 0; kk < HD; ++kk) {
-            const uint4 mw = __ldg(reinterpret_cast<const uint4*>(mh + kk * HD));
-            const float mb[8] = {bf_lo(mw.x), bf_hi(mw.x), bf_lo(mw.y), bf_hi(mw.y),
-                                 bf_lo(mw.z), bf_hi(mw.z), bf_lo(mw.w), bf_hi(mw.w)};
+            for (int x = 0; x < 4; ++x) acc[nt][x] = 0.f;
+        const unsigned short* mh = reinterpret_cast<const unsigned short*>(metric) + (size_t)h * HD * HD;
+        const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(sK + (16 * mt + (lane & 15)) * KS + (lane >> 4) * 8);
 #pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const float kv = __bfloat162float(sK[(4 * ty + a) * KS + kk]);
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(a_addr + ks * 32, a0, a1, a2, a3);
 #pragma unroll
-                for (int b = 0; b < 8; ++b) acc[a][b] = fmaf(kv, mb[b], acc[a][b]);
+            for (int nt = 0; nt < 8; ++nt) {
+                const int n0 = 64 * nh + 8 * nt + g, k0 = ks * 16 + 2 * tg;
+                // B[k][n] = M[k][n]: the pair (k0, k0 + 1) of column n0 sits in two rows of the row-major metric
+                const uint32_t b0 = (uint32_t)__ldg(mh + k0 * HD + n0) | ((uint32_t)__ldg(mh + (k0 + 1) * HD + n0) << 16);
+                const uint32_t b1 = (uint32_t)__ldg(mh + (k0 + 8) * HD + n0) | ((uint32_t)__ldg(mh + (k0 + 9) * HD + n0) << 16);
+                mma16816(acc[nt], a0, a1, a2, a3, b0, b1);
             }
         }
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
-#pragma unroll
-            for (int b = 0; b < 8; ++b) sX[(4 * ty + a) * XS + 8 * tx + b] = acc[a][b];
+        for (int nt = 0; nt < 8; ++nt) {
+            const int col = 64 * nh + 8 * nt + 2 * tg;
+            *reinterpret_cast<float2*>(sX + (16 * mt + g) * XS + col) = make_float2(acc[nt][0], acc[nt][1]);
+            *reinterpret_cast<float2*>(sX + (16 * mt + g + 8) * XS + col) = make_float2(acc[nt][2], acc[nt][3]);
+        }
     }
-    // probe scores: thread -> probes 4 py .., tokens 4 tx ..
     {
-        const int py = tid >> 4, tx = tid & 15;
+        // probe scores: probes 16 mt .. +15 (A, from global), tokens 32 nh .. +31 (B = K rows, from shared memory)
         float acc[4][4];
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
+        for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
-            for (int b = 0; b < 4; ++b) acc[a][b] = 0.f;
-        const __nv_bfloat16* ph = probes + ((size_t)h * NP + 4 * py) * HD;
-        for (int d = 0; d < HD; d += 2) {
-            float pa[4][2], kb[4][2];
+            for (int x = 0; x < 4; ++x) acc[nt][x] = 0.f;
+        const __nv_bfloat16* p0 = probes + ((size_t)h * NP + 16 * mt + g) * HD + 2 * tg;
 #pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const uint32_t pw = __ldg(reinterpret_cast<const uint32_t*>(ph + a * HD + d));
-                pa[a][0] = bf_lo(pw); pa[a][1] = bf_hi(pw);
-                const uint32_t kw = *reinterpret_cast<const uint32_t*>(sK + (4 * tx + a) * KS + d);
-                kb[a][0] = bf_lo(kw); kb[a][1] = bf_hi(kw);
+        for (int ks = 0; ks < 8; ++ks) {
+            const uint32_t a0 = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16));
+            const uint32_t a1 = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16));
+            const uint32_t a2 = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 8));
+            const uint32_t a3 = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16 + 8));
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const __nv_bfloat16* kr = sK + (32 * nh + 8 * nt + g) * KS + ks * 16 + 2 * tg;
+                mma16816(acc[nt], a0, a1, a2, a3, *reinterpret_cast<const uint32_t*>(kr),
+                         *reinterpret_cast<const uint32_t*>(kr + 8));
             }
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                for (int b = 0; b < 4; ++b) acc[a][b] = fmaf(pa[a][1], kb[b][1], fmaf(pa[a][0], kb[b][0], acc[a][b]));
         }
 #pragma unroll
-        for (int a = 0; a < 4; ++a)
-#pragma unroll
-            for (int b = 0; b < 4; ++b) sP[(4 * py + a) * PS + 4 * tx + b] = acc[a][b];
+        for (int nt = 0; nt < 4; ++nt) {
+            const int col = 32 * nh + 8 * nt + 2 * tg;
+            sP[(16 * mt + g) * PS + col] = acc[nt][0];
+            sP[(16 * mt + g) * PS + col + 1] = acc[nt][1];
+            sP[(16 * mt + g + 8) * PS + col] = acc[nt][2];
+            sP[(16 * mt + g + 8) * PS + col + 1] = acc[nt][3];
+        }
     }
     __syncthreads();
-    // each probe's softmax over the block's valid tokens (natural exponent)
-    if (tid < NP) {
-        float* row = sP + tid * PS;
+    // each probe's softmax over the block's valid tokens (natural exponent): four threads per probe, 16 tokens each
+    {
+        float* row = sP + (tid >> 2) * PS + (tid & 3) * 16;
+        const int t0 = (tid & 3) * 16;
         float mx = -INFINITY;
-        for (int t = 0; t < nvalid; ++t) mx = fmaxf(mx, row[t]);
-        float sum = 0.f;
-        for (int t = 0; t < 64; ++t) {
-            const float e = t < nvalid ? expf(row[t] - mx) : 0.f;
-            row[t] = e;
-            sum += e;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) mx = (t0 + t < nvalid) ? fmaxf(mx, row[t]) : mx;
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        float e[16], sum = 0.f;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) {
+            e[t] = (t0 + t < nvalid) ? expf(row[t] - mx) : 0.f;
+            sum += e[t];
         }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         const float inv = 1.0f / sum;
-        for (int t = 0; t < 64; ++t) row[t] *= inv;
+#pragma unroll
+        for (int t = 0; t < 16; ++t) row[t] = e[t] * inv;
+    }
+    __syncthreads();
+    // token weights: sum over the probes (four partial sums of 16 probes, added in a fixed order)
+    {
+        const int t = tid & 63, qp = tid >> 6;
+        float sacc = 0.f;
+#pragma unroll
+        for (int p = 0; p < 16; ++p) sacc += sP[(16 * qp + p) * PS + t];
+        wpart[qp * 64 + t] = sacc;
     }
     __syncthreads();
     if (tid < 64) {
-        float s = 0.f;
-        for (int p = 0; p < NP; ++p) s += sP[p * PS + tid];
-        w[tid] = tid < nvalid ? s * ((float)nvalid / (float)NP) : 0.f;
+        const float sacc = (wpart[tid] + wpart[64 + tid]) + (wpart[128 + tid] + wpart[192 + tid]);
+        w[tid] = tid < nvalid ? sacc * ((float)nvalid / (float)NP) : 0.f;
         lab[tid] = tid >> 4;
     }
     __syncthreads();
 
-    // weighted centroids of the current labels; keep_old: an emptied cluster keeps its centroid
+    // weighted centroids of the current labels (thread -> cluster tid / 64, dims 2 (tid % 64), +1); keep_old: an emptied
+    // cluster keeps its centroid. Also the cluster weights and the squared norms of the centroids.
     auto update_centroids = [&](bool keep_old) {
-        if (tid < 4) {
-            float s = 0.f;
-            for (int t = 0; t < nvalid; ++t) s += (lab[t] == tid) ? w[t] : 0.f;
-            cw[tid] = s;
+        const int c = tid >> 6, d = 2 * (tid & 63);
+        float s0 = 0.f, s1 = 0.f, ws = 0.f;
+        for (int t = 0; t < nvalid; ++t) {
+            const float wt = (lab[t] == c) ? w[t] : 0.f;
+            const float2 x = *reinterpret_cast<const float2*>(sX + t * XS + d);
+            s0 = fmaf(wt, x.x, s0);
+            s1 = fmaf(wt, x.y, s1);
+            ws += wt;
         }
+        float c0, c1;
+        if (!keep_old || ws > 0.f) {
+            const float inv = 1.0f / fmaxf(ws, 1e-6f);
+            c0 = s0 * inv; c1 = s1 * inv;
+            cen[c * XS + d] = c0;
+            cen[c * XS + d + 1] = c1;
+        } else {
+            c0 = cen[c * XS + d]; c1 = cen[c * XS + d + 1];
+        }
+        float nn = c0 * c0 + c1 * c1;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) nn += __shfl_xor_sync(0xffffffffu, nn, o);
+        if (lane == 0) wpart[warp] = nn;              // warps 2c, 2c + 1 hold cluster c
+        if ((tid & 63) == 0) cw[c] = ws;
         __syncthreads();
-        for (int e = tid; e < 4 * HD; e += 256) {
-            const int c = e >> 7, d = e & 127;
-            float s = 0.f;
-            for (int t = 0; t < nvalid; ++t) s += (lab[t] == c) ? w[t] * sX[t * XS + d] : 0.f;
-            if (!keep_old || cw[c] > 0.f) cen[c * XS + d] = s / fmaxf(cw[c], 1e-6f);
-        }
+        if (tid < 4) cnorm[tid] = wpart[2 * tid] + wpart[2 * tid + 1];
         __syncthreads();
     };
     update_centroids(false);
     for (int it = 0; it < iters; ++it) {
         // thread -> (token tid / 4, cluster tid % 4)
         const int t = tid >> 2, c = tid & 3;
-        float dot = 0.f, cc = 0.f;
-        for (int d = 0; d < HD; ++d) {
-            const float cv = cen[c * XS + d];
-            dot = fmaf(sX[t * XS + d], cv, dot);
-            cc = fmaf(cv, cv, cc);
+        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+        const float* xr = sX + t * XS;
+        const float* cr = cen + c * XS;
+#pragma unroll 8
+        for (int d = 0; d < HD; d += 4) {
+            const float4 x = *reinterpret_cast<const float4*>(xr + d);
+            const float4 y = *reinterpret_cast<const float4*>(cr + d);
+            d0 = fmaf(x.x, y.x, d0); d1 = fmaf(x.y, y.y, d1); d2 = fmaf(x.z, y.z, d2); d3 = fmaf(x.w, y.w, d3);
         }
-        float dist = cw[c] > 0.f ? cc - 2.0f * dot : INFINITY;
+        const float dot = (d0 + d1) + (d2 + d3);
+        float dist = cw[c] > 0.f ? cnorm[c] - 2.0f * dot : INFINITY;
         int best = c;
         // first minimum among the four clusters of this token (lanes 4 t' .. 4 t' + 3)
 #pragma unroll
@@ -314,18 +371,18 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     __syncthreads();
     {
         const int which = tid >> 7, d = tid & 127;
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+        const __nv_bfloat16* vp = v + ((size_t)(j * 64) * H + h) * HD + d;
         for (int t = 0; t < nvalid; ++t) {
-            const float x = which ? __bfloat162float(v[((size_t)(j * 64 + t) * H + h) * HD + d])
-                                  : __bfloat162float(sK[t * KS + d]);
+            const float x = which ? __bfloat162float(vp[(size_t)t * H * HD]) : __bfloat162float(sK[t * KS + d]);
             const int l = lab[t];
-            s[0] += l == 0 ? x : 0.f; s[1] += l == 1 ? x : 0.f; s[2] += l == 2 ? x : 0.f; s[3] += l == 3 ? x : 0.f;
+            sacc[0] += l == 0 ? x : 0.f; sacc[1] += l == 1 ? x : 0.f; sacc[2] += l == 2 ? x : 0.f; sacc[3] += l == 3 ? x : 0.f;
         }
         __nv_bfloat16* o = (which ? v4 : k4) + ((size_t)h * nb4 + j * 4) * HD + d;
 #pragma unroll
-        for (int c = 0; c < 4; ++c) o[c * HD] = __float2bfloat16_rn(s[c] * (1.0f / fmaxf(s_cnt[c], 1.0f)));
+        for (int c = 0; c < 4; ++c) o[c * HD] = __float2bfloat16_rn(sacc[c] * (1.0f / fmaxf(s_cnt[c], 1.0f)));
         __nv_bfloat16* mo = which ? vm : km;
-        if (mo) mo[((size_t)j * H + h) * HD + d] = __float2bfloat16_rn(((s[0] + s[1]) + (s[2] + s[3])) / (float)nvalid);
+        if (mo) mo[((size_t)j * H + h) * HD + d] = __float2bfloat16_rn(((sacc[0] + sacc[1]) + (sacc[2] + sacc[3])) / (float)nvalid);
     }
 }
 

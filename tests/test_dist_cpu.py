@@ -1,0 +1,70 @@
+"""Head sharding across ranks, on CPU with 2 gloo processes: the heads are divided without overlap, every rank regenerates
+exactly its own (branch, head) shard from the seeds, and the whole-job numbers that bench.py reports (sum of work, max of
+time) come out of the collectives as expected. No GPU and no data-path collective is involved."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from self_trainable_or_free_attn_b200 import synthetic
+
+GRID, HEADS = (2, 4, 8), 5           # 64 tokens, 5 heads: an uneven split over 2 ranks
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    heads = synthetic.shard_heads(HEADS, rank, world)
+    q, k, v = synthetic.branch_qkv(GRID, 0, 1, heads, "cpu")
+    # what bench.py reduces: per-rank work is summed, per-rank time is maximised
+    stats = torch.tensor([float(len(heads)), 10.0 + rank], dtype=torch.float64)
+    total, slowest = stats.clone(), stats.clone()
+    dist.all_reduce(total, op=dist.ReduceOp.SUM)
+    dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+    gathered = [None] * world
+    dist.all_gather_object(gathered, heads)
+    torch.save({"heads": heads, "q": q, "k": k, "v": v, "total": total, "slowest": slowest, "all": gathered},
+               os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_two_ranks_cover_all_heads_and_regenerate_their_shards(tmp_path):
+    world = 2
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    ranks = [torch.load(tmp_path / f"rank{r}.pt") for r in range(world)]
+    assert ranks[0]["heads"] == [0, 1, 2] and ranks[1]["heads"] == [3, 4]
+    assert ranks[0]["all"] == [[0, 1, 2], [3, 4]]
+    full = synthetic.branch_qkv(GRID, 0, 1, list(range(HEADS)), "cpu")
+    for name, ref in zip("qkv", full):
+        got = torch.cat([r[name] for r in ranks], dim=2)
+        assert torch.equal(got, ref)
+    for r in ranks:
+        assert r["total"].tolist() == [5.0, 21.0] and r["slowest"].tolist() == [3.0, 11.0]
+
+
+@pytest.mark.parametrize("heads,world", [(40, 1), (40, 2), (40, 4), (40, 8), (12, 8), (24, 8), (3, 4)])
+def test_shard_heads_is_a_balanced_partition(heads, world):
+    parts = [synthetic.shard_heads(heads, r, world) for r in range(world)]
+    assert sum(parts, []) == list(range(heads))
+    sizes = [len(p) for p in parts]
+    assert max(sizes) - min(sizes) <= 1
+
+
+def test_branches_of_a_head_share_structure_but_not_noise():
+    a = synthetic.head_qkv(GRID, 2, 0, 3, "cpu", dtype=torch.float32)
+    b = synthetic.head_qkv(GRID, 2, 1, 3, "cpu", dtype=torch.float32)
+    again = synthetic.head_qkv(GRID, 2, 0, 3, "cpu", dtype=torch.float32)
+    assert all(torch.equal(x, y) for x, y in zip(a, again))
+    assert not torch.equal(a[0], b[0])
+    prev = synthetic.head_qkv(GRID, 2, 0, 3, "cpu", prev=True, dtype=torch.float32)
+    assert 0 < (prev[0] - a[0]).abs().max() < 0.2 and torch.equal(prev[2], a[2])

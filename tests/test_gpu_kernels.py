@@ -257,7 +257,10 @@ def test_pipeline_matches_oracle(K, L, H, density):
     reps.build(q, k, v)
     kr, vr, lc, _ = R.representatives(q, k, v, 10, reps._metric, reps._probes)
     same = ((lc == reps.log_counts) | ((lc - reps.log_counts).abs() < 1e-6)).view(H, nb + 1, 4).all(-1)
-    assert same.float().mean() > 0.9
+    # cluster labels are decided by float32 comparisons: a near-tie may move a token in a few blocks
+    differing = int((~same).sum())
+    assert differing <= max(1, same.numel() // 10), (differing, torch.exp2(lc).view(H, nb + 1, 4)[~same],
+                                                      torch.exp2(reps.log_counts).view(H, nb + 1, 4)[~same])
     assert rel_l2(reps.k.view(H, nb + 1, 4, 128)[same], kr.view(H, nb + 1, 4, 128)[same]) <= 5e-3
     out2, lse2, flags2 = _outputs(L, H, q)
     mass2 = torch.zeros(H, nq, nb, device=DEV)
