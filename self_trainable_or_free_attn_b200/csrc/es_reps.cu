@@ -22,54 +22,100 @@ __device__ __forceinline__ float bf_lo(uint32_t w) { return __uint_as_float(w <<
 __device__ __forceinline__ float bf_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
 
 // ------------------------------------------------------------------------------------------------ Gram partials
-// parts[h][split] = sum over the split's rows of q_r q_r^T. Thread (ty, tx) owns an 8 x 8 patch.
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// 16-byte asynchronous copy global -> shared; `bytes` = 0 fills the destination with zeros
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, int bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// parts[h][split] = sum over the split's rows of q_r q_r^T (bf16 products, float32 sums). The rows stream through two
+// 64-row shared-memory tiles (cp.async); both MMA operands are transposed views of the same tile (ldmatrix.trans): warp
+// (wm, wn) owns the 32 x 64 patch at (32 wm, 64 wn) of the 128 x 128 result.
+constexpr int GS = 136;           // bf16 row stride of a row tile: 272 B, conflict-free for ldmatrix
 __global__ void __launch_bounds__(256)
 gram_kernel(const __nv_bfloat16* __restrict__ q, float* __restrict__ parts, int L, int H, int rows_per_split,
             int nsplit) {
-    __shared__ __align__(16) float rows[32][HD];
-    const int h = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x;
-    const int ty = tid >> 4, tx = tid & 15;
-    float acc[8][8];
+    __shared__ __align__(16) __nv_bfloat16 tile[2][64 * GS];
+    const int h = blockIdx.x, sp = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int wm = warp >> 1, wn = warp & 1, g = lane >> 2, tg = lane & 3;
+    float acc[2][8][4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+        for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[i][j][x] = 0.f;
     const int r_begin = sp * rows_per_split, r_end = min(L, r_begin + rows_per_split);
-    for (int r0 = r_begin; r0 < r_end; r0 += 32) {
-        // 32 rows x 256 B: thread -> (row tid / 8, two 16-byte pieces)
+    const int nchunk = (r_end - r_begin + 63) / 64;
+    auto load = [&](int c, int buf) {
+        // 64 rows x 256 B: thread -> row tid / 4 (+ 0), four 16-byte pieces
 #pragma unroll
-        for (int x = 0; x < 2; ++x) {
-            const int rr = tid >> 3, c16 = (tid & 7) + 8 * x;
-            const int row = r0 + rr;
-            uint4 w = make_uint4(0, 0, 0, 0);
-            if (row < r_end) w = *reinterpret_cast<const uint4*>(q + ((size_t)row * H + h) * HD + c16 * 8);
-            float* d = &rows[rr][c16 * 8];
-            d[0] = bf_lo(w.x); d[1] = bf_hi(w.x); d[2] = bf_lo(w.y); d[3] = bf_hi(w.y);
-            d[4] = bf_lo(w.z); d[5] = bf_hi(w.z); d[6] = bf_lo(w.w); d[7] = bf_hi(w.w);
+        for (int x = 0; x < 4; ++x) {
+            const int rr = tid >> 2, c16 = (tid & 3) * 4 + x;
+            const int row = r_begin + c * 64 + rr;
+            const bool okr = row < r_end;
+            cp_async16_zfill((uint32_t)__cvta_generic_to_shared(&tile[buf][rr * GS + c16 * 8]),
+                             q + ((size_t)(okr ? row : 0) * H + h) * HD + c16 * 8, okr ? 16 : 0);
         }
+        cp_async_commit();
+    };
+    if (nchunk > 0) load(0, 0);
+    const int lj = lane & 7, lm = lane >> 3;
+    for (int c = 0; c < nchunk; ++c) {
+        if (c + 1 < nchunk) { load(c + 1, (c + 1) & 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
         __syncthreads();
-#pragma unroll 4
-        for (int r = 0; r < 32; ++r) {
-            const float4 a0 = *reinterpret_cast<const float4*>(&rows[r][8 * ty]);
-            const float4 a1 = *reinterpret_cast<const float4*>(&rows[r][8 * ty + 4]);
-            const float4 b0 = *reinterpret_cast<const float4*>(&rows[r][8 * tx]);
-            const float4 b1 = *reinterpret_cast<const float4*>(&rows[r][8 * tx + 4]);
-            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+        const uint32_t tb = (uint32_t)__cvta_generic_to_shared(&tile[c & 1][0]);
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+        for (int ks = 0; ks < 4; ++ks) {
+            const int k0 = ks * 16;
+            uint32_t a[2][4];
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+            for (int i = 0; i < 2; ++i) {
+                // A[m][k] = tile[k][m]: matrices (m lo, k lo), (m hi, k lo), (m lo, k hi), (m hi, k hi)
+                const int row = k0 + lj + (lm >> 1) * 8, col = 32 * wm + 16 * i + (lm & 1) * 8;
+                ldmatrix_x4_trans(tb + (uint32_t)(row * GS + col) * 2, a[i][0], a[i][1], a[i][2], a[i][3]);
+            }
+#pragma unroll
+            for (int jp = 0; jp < 4; ++jp) {
+                // B[k][n] = tile[k][n]: matrices (k lo, n0), (k hi, n0), (k lo, n0 + 8), (k hi, n0 + 8)
+                const int row = k0 + lj + (lm & 1) * 8, col = 64 * wn + 16 * jp + (lm >> 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(tb + (uint32_t)(row * GS + col) * 2, b0, b1, b2, b3);
+#pragma unroll
+                for (int i = 0; i < 2; ++i) {
+                    mma16816(acc[i][2 * jp], a[i][0], a[i][1], a[i][2], a[i][3], b0, b1);
+                    mma16816(acc[i][2 * jp + 1], a[i][0], a[i][1], a[i][2], a[i][3], b2, b3);
+                }
+            }
         }
         __syncthreads();
     }
     float* out = parts + ((size_t)h * nsplit + sp) * HD * HD;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        float4* o = reinterpret_cast<float4*>(out + (8 * ty + i) * HD + 8 * tx);
-        o[0] = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-        o[1] = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
-    }
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int m = 32 * wm + 16 * i + g, nn = 64 * wn + 8 * j + 2 * tg;
+            *reinterpret_cast<float2*>(out + m * HD + nn) = make_float2(acc[i][j][0], acc[i][j][1]);
+            *reinterpret_cast<float2*>(out + (m + 8) * HD + nn) = make_float2(acc[i][j][2], acc[i][j][3]);
+        }
 }
 
 // ------------------------------------------------------------------------------------------------ metric
@@ -153,28 +199,19 @@ probe_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ pr
 constexpr int KS = 136;           // bf16 row stride of the K tile: 272 B, so the 8 rows of an ldmatrix hit distinct banks
 constexpr int XS = 132;           // float row stride of X and of the centroids
 constexpr int PS = 65;            // float row stride of the probe scores
-constexpr int KM_SMEM = 64 * KS * 2 + 64 * XS * 4 + 64 * PS * 4 + 4 * XS * 4 + 4 * 64 * 4 + 64 * 4 + 64 * 4;
+constexpr int MS = 136;           // bf16 row stride of the metric in shared memory
+constexpr int KM_BLOCKS = 4;      // kv blocks per CTA: the metric is loaded into shared memory once for all of them
+constexpr int KM_SMEM = 128 * MS * 2 + 64 * KS * 2 + 64 * XS * 4 + 64 * PS * 4 + 4 * XS * 4 + 4 * 64 * 4 + 64 * 4 + 64 * 4;
 
-__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                                         uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void ldmatrix_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
-}
-
-__global__ void __launch_bounds__(256, 3)
+__global__ void __launch_bounds__(256, 2)
 kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
               const __nv_bfloat16* __restrict__ metric, const __nv_bfloat16* __restrict__ probes,
               __nv_bfloat16* __restrict__ k4, __nv_bfloat16* __restrict__ v4, float* __restrict__ c4,
               __nv_bfloat16* __restrict__ km, __nv_bfloat16* __restrict__ vm, int L, int H, int nb4, int iters) {
     extern __shared__ __align__(16) uint8_t raw[];
-    __nv_bfloat16* sK = reinterpret_cast<__nv_bfloat16*>(raw);                     // [64][KS]
-    float* sX = reinterpret_cast<float*>(raw + 64 * KS * 2);                        // [64][XS]
+    __nv_bfloat16* sM = reinterpret_cast<__nv_bfloat16*>(raw);                     // [128][MS] the head's metric
+    __nv_bfloat16* sK = sM + 128 * MS;                                             // [64][KS]
+    float* sX = reinterpret_cast<float*>(raw + 128 * MS * 2 + 64 * KS * 2);         // [64][XS]
     float* sP = sX + 64 * XS;                                                       // [64 probes][PS]
     float* cen = sP + 64 * PS;                                                      // [4][XS]
     float* wpart = cen + 4 * XS;                                                    // [4][64]
@@ -183,17 +220,28 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     __shared__ float cw[4], cnorm[4];
     __shared__ int s_changed;
     __shared__ float s_cnt[4];
-    const int j = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tg = lane & 3;
+    const int nb = (L + 63) / 64;
+    // the metric of this head: 128 x 128 bf16, once per CTA
+    for (int e = tid; e < 128 * 16; e += 256) {
+        const int r = e >> 4, c16 = e & 15;
+        cp_async16_zfill((uint32_t)__cvta_generic_to_shared(sM + r * MS + c16 * 8),
+                         metric + ((size_t)h * HD + r) * HD + c16 * 8, 16);
+    }
+    cp_async_commit();
+  for (int j = blockIdx.x * KM_BLOCKS; j < min(nb, (int)(blockIdx.x + 1) * KM_BLOCKS); ++j) {
     const int nvalid = min(L - j * 64, 64);
-
+    __syncthreads();                       // the previous block's readers of the shared tiles are done
     // K tile (rows past L are zero)
     for (int e = tid; e < 64 * 16; e += 256) {
         const int r = e >> 4, c16 = e & 15;
-        uint4 x = make_uint4(0, 0, 0, 0);
-        if (r < nvalid) x = *reinterpret_cast<const uint4*>(k + ((size_t)(j * 64 + r) * H + h) * HD + c16 * 8);
-        *reinterpret_cast<uint4*>(sK + r * KS + c16 * 8) = x;
+        const bool okr = r < nvalid;
+        cp_async16_zfill((uint32_t)__cvta_generic_to_shared(sK + r * KS + c16 * 8),
+                         k + ((size_t)(j * 64 + (okr ? r : 0)) * H + h) * HD + c16 * 8, okr ? 16 : 0);
     }
+    cp_async_commit();
+    cp_async_wait<0>();
     __syncthreads();
 
     const int mt = warp & 3, nh = warp >> 2;
@@ -206,19 +254,22 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
             for (int x = 0; x < 4; ++x) acc[nt][x] = 0.f;
-        const unsigned short* mh = reinterpret_cast<const unsigned short*>(metric) + (size_t)h * HD * HD;
         const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(sK + (16 * mt + (lane & 15)) * KS + (lane >> 4) * 8);
+        const uint32_t m_addr = (uint32_t)__cvta_generic_to_shared(sM);
+        const int lj = lane & 7, lm = lane >> 3;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
             uint32_t a0, a1, a2, a3;
             ldmatrix_x4(a_addr + ks * 32, a0, a1, a2, a3);
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt) {
-                const int n0 = 64 * nh + 8 * nt + g, k0 = ks * 16 + 2 * tg;
-                // B[k][n] = M[k][n]: the pair (k0, k0 + 1) of column n0 sits in two rows of the row-major metric
-                const uint32_t b0 = (uint32_t)__ldg(mh + k0 * HD + n0) | ((uint32_t)__ldg(mh + (k0 + 1) * HD + n0) << 16);
-                const uint32_t b1 = (uint32_t)__ldg(mh + (k0 + 8) * HD + n0) | ((uint32_t)__ldg(mh + (k0 + 9) * HD + n0) << 16);
-                mma16816(acc[nt], a0, a1, a2, a3, b0, b1);
+            for (int np = 0; np < 4; ++np) {
+                // B[k][n] = M[k][n], row-major in shared memory: transposed 8 x 8 loads, matrices (k lo, n0), (k hi, n0),
+                // (k lo, n0 + 8), (k hi, n0 + 8)
+                const int row = ks * 16 + lj + (lm & 1) * 8, col = 64 * nh + 16 * np + (lm >> 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(m_addr + (uint32_t)(row * MS + col) * 2, b0, b1, b2, b3);
+                mma16816(acc[2 * np], a0, a1, a2, a3, b0, b1);
+                mma16816(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
             }
         }
 #pragma unroll
@@ -295,6 +346,16 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
         w[tid] = tid < nvalid ? sacc * ((float)nvalid / (float)NP) : 0.f;
         lab[tid] = tid >> 4;
     }
+    // The probe scores are dead now: their area receives the V tile (64 x 128 bf16), copied asynchronously while the
+    // Lloyd iterations run, so the final cluster means do not wait on global memory.
+    __nv_bfloat16* sV = reinterpret_cast<__nv_bfloat16*>(sP);
+    for (int e = tid; e < 64 * 16; e += 256) {
+        const int r = e >> 4, c16 = e & 15;
+        const bool okr = r < nvalid;
+        cp_async16_zfill((uint32_t)__cvta_generic_to_shared(sV + r * HD + c16 * 8),
+                         v + ((size_t)(j * 64 + (okr ? r : 0)) * H + h) * HD + c16 * 8, okr ? 16 : 0);
+    }
+    cp_async_commit();
     __syncthreads();
 
     // weighted centroids of the current labels (thread -> cluster tid / 64, dims 2 (tid % 64), +1); keep_old: an emptied
@@ -368,13 +429,13 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
         s_cnt[tid] = (float)n;
         c4[(size_t)h * nb4 + j * 4 + tid] = n > 0 ? log2f((float)n) : -INFINITY;
     }
+    cp_async_wait<0>();
     __syncthreads();
     {
         const int which = tid >> 7, d = tid & 127;
         float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-        const __nv_bfloat16* vp = v + ((size_t)(j * 64) * H + h) * HD + d;
         for (int t = 0; t < nvalid; ++t) {
-            const float x = which ? __bfloat162float(vp[(size_t)t * H * HD]) : __bfloat162float(sK[t * KS + d]);
+            const float x = which ? __bfloat162float(sV[t * HD + d]) : __bfloat162float(sK[t * KS + d]);
             const int l = lab[t];
             sacc[0] += l == 0 ? x : 0.f; sacc[1] += l == 1 ? x : 0.f; sacc[2] += l == 2 ? x : 0.f; sacc[3] += l == 3 ? x : 0.f;
         }
@@ -384,6 +445,7 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
         __nv_bfloat16* mo = which ? vm : km;
         if (mo) mo[((size_t)j * H + h) * HD + d] = __float2bfloat16_rn(((sacc[0] + sacc[1]) + (sacc[2] + sacc[3])) / (float)nvalid);
     }
+  }
 }
 
 }  // namespace es
@@ -444,7 +506,7 @@ extern "C" int es_reps_kmeans(const void* k, const void* v, const void* metric, 
         if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
         attr = true;
     }
-    kmeans_kernel<<<dim3(nb, H), 256, KM_SMEM, (cudaStream_t)stream>>>(
+    kmeans_kernel<<<dim3((nb + KM_BLOCKS - 1) / KM_BLOCKS, H), 256, KM_SMEM, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)metric, (const __nv_bfloat16*)probes,
         (__nv_bfloat16*)k_rep, (__nv_bfloat16*)v_rep, log_counts, (__nv_bfloat16*)k_mean, (__nv_bfloat16*)v_mean, L, H,
         (nb + 1) * 4, iters);
