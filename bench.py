@@ -213,7 +213,9 @@ def main():
 
     # ---- warm-up, then the device-resident timed region
     run_steps(attn, inputs, 2, args.warmup)
-    timer = K.KernelTimer(["sparse_attention"])
+    names = ["sparse_attention", "block_attention", "exact_fallback", "compensate_fallback", "block_means", "select_blocks",
+             "estimate_skipped", "full_step_scales", "reps_build"]
+    timer = K.KernelTimer(names)
     sampler = ClockSampler(local)
     barrier()
     K.set_kernel_timer(timer)
@@ -316,6 +318,7 @@ def main():
         "e2e": {"value": flops_all / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
+        "kernel_ms_per_step": {n: round(sum(timer.ms(n)) / args.steps, 3) for n in names if timer.events[n]},
         "roofline": {"bound": "tensor", "kernel": "attention_kernel<false> (es_sparse_attention)", "achieved": achieved,
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                      "peak_source": f"bf16_tflops_sustained of {peaks['source']}", "ms_per_launch": k_ms,

@@ -25,7 +25,8 @@ int es_abi_version(void);
 /* Kernels launched by this library in this process so far. */
 long long es_launch_count(void);
 /* Synchronises the current device, reads its status word into *status_out and clears it. 0 = fine; any other value is
- * the code of a bounded in-kernel wait that gave up (the kernel returned early and its outputs are invalid). */
+ * (code of the bounded in-kernel wait that gave up) + 1000 * (its CTA index): that kernel returned early, its outputs are
+ * invalid, and attention kernels launched before the word is read return at once. */
 int es_device_status(int32_t* status_out);
 
 /* Exact attention over a list of 64-token blocks at a fixed softmax offset, with per-block masses.
@@ -123,7 +124,8 @@ int es_reps_kmeans(const void* k, const void* v, const void* metric, const void*
 /* Debugging aid (no counterpart in the reference): with a non-NULL device buffer of es_debug_trace_words() zeroed
  * 32-bit words, the attention kernels launched afterwards write clock stamps of the pipeline stages of their first CTAs
  * into it: [cta < 8][role: 0 softmax thread 0, 1 MMA thread][iteration < 64][half][8 stamps], cycles since CTA start.
- * NULL switches it off. */
+ * NULL switches it off. The last 512 words of the buffer are a report area of debug builds: per SM the last stage a CTA
+ * reached and the last wait that gave up; with host-mapped memory the host can read them while a kernel is running. */
 int es_debug_set_trace(void* buffer);
 int es_debug_trace_words(void);
 

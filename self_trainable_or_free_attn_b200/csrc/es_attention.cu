@@ -52,7 +52,7 @@ struct Ctl {
     uint64_t full[NSLOT], empty[NSLOT];
     uint64_t sfull[2], pfull[2];
     uint64_t ofull, drain;
-    uint64_t massbar, flagbar, lbar;   // softmax warps -> the thread(s) that combine their partial results
+    uint64_t massbar[4], flagbar, lbar;   // softmax warps -> the thread(s) that combine their partial results
     uint64_t sweepbar;                 // K load warp -> V load warp: the fallback sweep's tiles have all been issued
     uint32_t tmem_base;
     int abort;
@@ -65,6 +65,7 @@ static_assert(sizeof(Ctl) <= 3072, "control block");
 
 struct AttnArgs {
     const __nv_bfloat16* q;      // (L, H, 128)
+    const uint8_t* keep;         // (H, nq, nb), compensation mode only
     __nv_bfloat16* out;
     const int* counts;           // (nq, H)
     const int* blocks;           // (nq, H, nk) ascending block ids
@@ -148,21 +149,24 @@ __device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
 #endif
 __device__ __forceinline__ constexpr bool emulate_pair(int j) { return (ES_EMU_PATTERN >> (j & 7)) & 1; }
 
-template <bool FALLBACK>
+template <int MODE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                  const __grid_constant__ CUtensorMap tmKm, const __grid_constant__ CUtensorMap tmVm, const AttnArgs a) {
+    constexpr bool FALLBACK = MODE == 1;       // online-softmax recomputation of flagged tiles
+    constexpr bool COMPENSATE = MODE == 2;     // block-mean compensation of flagged tiles, added to out / lse in place
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const long long t_start = clock64();
     // adjacent CTAs are adjacent query tiles of one head: their kv lists overlap in L2
     const int qb = blockIdx.x % a.nq, h = blockIdx.x / a.nq;
     const int th_idx = qb * a.H + h;
-    if (FALLBACK) {
+    if (FALLBACK || COMPENSATE) {
         if (a.flags[th_idx] == 0) return;          // uniform over the CTA, before anything is allocated
     }
     // a wait has given up earlier (the status word is set until the host reads it): do not start more work
     if (*reinterpret_cast<volatile int*>(a.status) != 0) return;
 
+    if (tid == 0) dbg_stage(1);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + SMEM_CTL);
@@ -182,7 +186,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         }
         mbar_init(smem_u32(&ctl->ofull), 1);
         mbar_init(smem_u32(&ctl->drain), 1);
-        mbar_init(smem_u32(&ctl->massbar), 8);
+        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->massbar[i]), 8);
         mbar_init(smem_u32(&ctl->flagbar), 4);
         mbar_init(smem_u32(&ctl->lbar), NSOFT);
         mbar_init(smem_u32(&ctl->sweepbar), 1);
@@ -198,11 +202,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
+    if (tid == 0) dbg_stage(2);
 
-    const int n64 = a.counts[th_idx];
+    const int n64 = COMPENSATE ? 0 : a.counts[th_idx];
     const int n = (n64 + 1) >> 1;                     // exact iterations: pairs of 64-token blocks
     const int nvirt = FALLBACK ? 0 : a.nvirt;
-    const int nref = FALLBACK ? 0 : a.nref;
+    const int nref = (FALLBACK || COMPENSATE) ? 0 : a.nref;
     const int nt = n + nvirt + nref;
     const int* list = a.blocks + (size_t)th_idx * a.nk;
 
@@ -301,11 +306,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         uint32_t cslot = 0, cpar = 0, nQK[2] = {0, 0}, wP[2] = {0, 0};
         const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
         const uint32_t sfull0 = smem_u32(&ctl->sfull[0]), pfull0 = smem_u32(&ctl->pfull[0]);
-        bool ok = mbar_wait(smem_u32(&ctl->qfull), 0, abort_flag, a.status, 201);     // Q is in tensor memory
+        bool ok = mbar_wait_warp(smem_u32(&ctl->qfull), 0, abort_flag, a.status, 201);     // Q is in tensor memory
         // next tile of the ring: returns its slot
         auto take = [&](bool gathered) -> uint32_t {
             const uint32_t slot = cslot;
-            ok = ok && mbar_wait(full0 + 8 * slot, cpar, abort_flag, a.status, 202);
+            ok = ok && mbar_wait_warp(full0 + 8 * slot, cpar, abort_flag, a.status, 202);
             if (++cslot == NSLOT) { cslot = 0; cpar ^= 1; }
             if (gathered) fence_proxy_async_smem();    // cp.async gathers are generic-proxy writes
             return slot;
@@ -316,7 +321,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             const uint32_t slot = take(gathered);
             if (lane == 0) trace_put(a.trace, 1, ti, 5, t_start);
             while (ok && wP[buf] < nQK[buf]) {
-                ok = mbar_wait(pfull0 + 8 * buf, wP[buf] & 1, abort_flag, a.status, 203);
+                ok = mbar_wait_warp(pfull0 + 8 * buf, wP[buf] & 1, abort_flag, a.status, 203);
                 ++wP[buf];
             }
             if (!ok) return;
@@ -344,7 +349,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             if (lane == 0) trace_put(a.trace, 1, i, 0, t_start);
             const uint32_t slot = take(i >= n + nvirt);
             if (lane == 0) trace_put(a.trace, 1, i, 1, t_start);
-            ok = ok && mbar_wait(pfull0 + 8 * buf, wP[buf] & 1, abort_flag, a.status, 205);   // P(i) stored
+            ok = ok && mbar_wait_warp(pfull0 + 8 * buf, wP[buf] & 1, abort_flag, a.status, 205);   // P(i) stored
             if (lane == 0) trace_put(a.trace, 1, i, 2, t_start);
             if (!ok) break;
             ++wP[buf];
@@ -392,7 +397,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             mbar_arrive(smem_u32(&ctl->qfull));
         }
         float m = a.offset[(size_t)row * a.H + h];
-        uint32_t uS[2] = {0, 0}, uM = 0;
+        uint32_t uS[2] = {0, 0};
 
         if (FALLBACK) {
             float mx = -INFINITY;
@@ -400,7 +405,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 const int buf = i & 1, e = 2 * i + ch;
                 const bool has = e < n64;
                 const int blk = list[has ? e : e - 1];
-                ok = ok && mbar_wait(smem_u32(&ctl->sfull[buf]), uS[buf] & 1, abort_flag, a.status, 301);
+                ok = ok && mbar_wait_warp(smem_u32(&ctl->sfull[buf]), uS[buf] & 1, abort_flag, a.status, 301);
                 if (!ok) break;
                 ++uS[buf];
                 tc_fence_after();
@@ -418,7 +423,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             // the row maximum over both column halves
             ctl->m_part[ch][trow] = mx;
             mbar_arrive(smem_u32(&ctl->lbar));
-            ok = ok && mbar_wait(smem_u32(&ctl->lbar), 0, abort_flag, a.status, 306);
+            ok = mbar_wait_warp(smem_u32(&ctl->lbar), 0, abort_flag, a.status, 306) && ok;
             mx = fmaxf(ctl->m_part[0][trow], ctl->m_part[1][trow]);
             m = (mx == -INFINITY) ? 0.f : mx * a.scale_log2;
         }
@@ -427,19 +432,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         const int* rl = a.refine + (size_t)th_idx * a.rw;
         const float* lc = a.log_counts + (size_t)h * a.nb4;
         const int* bits = a.skip_bits + ((size_t)h * a.nq + qb) * a.nw;
-        const bool want_mass = !FALLBACK && a.mass != nullptr;
+        const bool want_mass = !FALLBACK && !COMPENSATE && a.mass != nullptr;
         const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
         // block id of this warp's column half in the exact iteration that comes next, loaded one iteration ahead
         int nblk = n > 0 ? list[ch < n64 ? ch : 0] : 0;
         // thread 0 stores the masses of an iteration at the start of the next one: by then the other warps' partial sums
         // have long arrived, so the store never holds back the warp that the others wait for
-        int pend_a = -1, pend_b = -1, pend_buf = 0;
+        int pend_a = -1, pend_b = -1, pend_i = 0;
         auto flush_mass = [&]() {
             if (tid == 0 && pend_a >= 0) {
-                ok = mbar_wait(smem_u32(&ctl->massbar), uM & 1, abort_flag, a.status, 304);
-                ++uM;
-                if (ok) {
-                    const float* mp = ctl->mass_part[pend_buf][0];
+                // one barrier and one set of partial sums per iteration modulo 4: a warp can reach iteration i + 4 only
+                // after every warp has finished iteration i + 1, so arrivals of different iterations never mix
+                if (mbar_wait(smem_u32(&ctl->massbar[pend_i & 3]), (pend_i >> 2) & 1, abort_flag, a.status, 304)) {
+                    const float* mp = ctl->mass_part[pend_i & 3][0];
                     float* mrow = a.mass + ((size_t)h * a.nq + qb) * a.nb;
                     mrow[pend_a] = ((mp[0] + mp[1]) + mp[2]) + mp[3];
                     if (pend_b >= 0) mrow[pend_b] = ((mp[4] + mp[5]) + mp[6]) + mp[7];
@@ -458,7 +463,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             }
             flush_mass();
             if (tid == 0) trace_put(a.trace, 0, i, 0, t_start);
-            ok = ok && mbar_wait(smem_u32(&ctl->sfull[buf]), uS[buf] & 1, abort_flag, a.status, 302);
+            ok = ok && mbar_wait_warp(smem_u32(&ctl->sfull[buf]), uS[buf] & 1, abort_flag, a.status, 302);
             if (!ok) break;
             if (tid == 0) trace_put(a.trace, 0, i, 1, t_start);
             ++uS[buf];
@@ -496,7 +501,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             } else if (pooled) {
                 // block-mean columns: column c of this half is block 128 cv + 64 ch + c; a set bit masks it
                 const int cv = i - n;
-                const uint32_t w0 = (uint32_t)bits[4 * cv + 2 * ch], w1 = (uint32_t)bits[4 * cv + 2 * ch + 1];
+                uint32_t w0, w1;
+                if (COMPENSATE) {
+                    // every block that was not kept (refined ones included) is compensated: bits from the keep mask
+                    const int b0 = 128 * cv + 64 * ch;
+                    const uint8_t* kp = a.keep + ((size_t)h * a.nq + qb) * a.nb + b0;
+                    w0 = 0; w1 = 0;
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) {
+                        w0 |= (uint32_t)(b0 + c >= a.nb ? 1 : kp[c] != 0) << c;
+                        w1 |= (uint32_t)(b0 + 32 + c >= a.nb ? 1 : kp[32 + c] != 0) << c;
+                    }
+                } else {
+                    w0 = (uint32_t)bits[4 * cv + 2 * ch];
+                    w1 = (uint32_t)bits[4 * cv + 2 * ch + 1];
+                }
                 const float2 off2 = make_float2(-m + 6.0f, -m + 6.0f);   // log2(64): a mean stands for its block's tokens
                 const int last_c = (a.nb - 1) - (128 * cv + 64 * ch);    // column of the (maybe shorter) last block
                 const float fix = a.tail_log2 - 6.0f;
@@ -505,6 +524,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                     float2 xv = __ffma2_rn(make_float2(__uint_as_float(s[2 * j]), __uint_as_float(s[2 * j + 1])), sc2, off2);
                     if (2 * j == last_c) xv.x += fix;
                     if (2 * j + 1 == last_c) xv.y += fix;
+                    if (COMPENSATE) { xv.x = fminf(xv.x, 100.0f); xv.y = fminf(xv.y, 100.0f); }   // triton_ops.py:275
                     float2 p = exp2_pair_mufu(xv);
                     const uint32_t w = j < 16 ? w0 : w1;
                     p.x = ((w >> ((2 * j) & 31)) & 1u) ? 0.f : p.x;
@@ -555,12 +575,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 for (int o = 16; o > 0; o >>= 1) pa += __shfl_xor_sync(0xffffffffu, pa, o);
                 if (lane == 0) {
                     ctl->mass_part[i & 3][ch][rq] = pa;
-                    mbar_arrive(smem_u32(&ctl->massbar));
+                    mbar_arrive(smem_u32(&ctl->massbar[i & 3]));
                 }
                 if (tid == 0) {
                     pend_a = blk;
                     pend_b = (2 * i + 1 < n64) ? list[2 * i + 1] : -1;
-                    pend_buf = i & 3;
+                    pend_i = i;
                 }
             }
         }
@@ -569,13 +589,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         // ---- epilogue: row sums of both column halves, then this thread's 64 columns of O
         ctl->l_part[ch][trow] = lsum.x + lsum.y;
         mbar_arrive(smem_u32(&ctl->lbar));
-        ok = ok && mbar_wait(smem_u32(&ctl->lbar), FALLBACK ? 1 : 0, abort_flag, a.status, 307);
+        ok = mbar_wait_warp(smem_u32(&ctl->lbar), FALLBACK ? 1 : 0, abort_flag, a.status, 307) && ok;
         const float l = ctl->l_part[0][trow] + ctl->l_part[1][trow];
-        const float lg = log2f(l);
-        if (nt > 0) ok = ok && mbar_wait(smem_u32(&ctl->ofull), 0, abort_flag, a.status, 303);
+        // compensation: out = (out + sum e v) / (1 + sum e), lse += log2(1 + sum e) (triton_ops.py:280-282)
+        const float lg = COMPENSATE ? log2f(1.0f + l) : log2f(l);
+        if (nt > 0) ok = mbar_wait_warp(smem_u32(&ctl->ofull), 0, abort_flag, a.status, 303) && ok;
         if (ok) {
             tc_fence_after();
-            const float inv = 1.0f / l;
+            const float inv = COMPENSATE ? 1.0f / (1.0f + l) : 1.0f / l;
             __nv_bfloat16* orow = a.out + ((size_t)row * a.H + h) * HD + 64 * ch;
 #pragma unroll
             for (int part = 0; part < 2; ++part) {
@@ -588,6 +609,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint4 w;
+                        if (COMPENSATE) {
+                            const uint4 old = *reinterpret_cast<const uint4*>(orow + 32 * part + c);
+                            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                o[c + 2 * e] = __float_as_uint(__uint_as_float(o[c + 2 * e]) + __uint_as_float(ow[e] << 16));
+                                o[c + 2 * e + 1] = __float_as_uint(__uint_as_float(o[c + 2 * e + 1]) + __uint_as_float(ow[e] & 0xFFFF0000u));
+                            }
+                        }
                         w.x = pack_bf16x2(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
                         w.y = pack_bf16x2(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
                         w.z = pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
@@ -601,7 +631,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             if (ch == 0) {
                 // rows past L keep the "no offset" value, as echosparse/kernels/sm120.py:96
                 a.lse[(size_t)row * a.H + h] = valid ? m + lg : 1e30f;
-                if (!FALLBACK) {
+                if (!FALLBACK && !COMPENSATE) {
                     // a tile whose row sums leave 2^[-th, th] is flagged and recomputed with online softmax
                     const bool bad = valid && !(lg >= -a.th && lg <= a.th);
                     const unsigned ballot = __ballot_sync(0xffffffffu, bad);
@@ -617,15 +647,15 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     }
 
     // ---------------------------------------------------------------- teardown
+    if (lane == 0) dbg_stage(3 + warp);
     __syncwarp();
     if ((warp == LOADK_WARP || warp == LOADV_WARP) && lane == 0 && *abort_flag) {
-        // a wait gave up somewhere: let the loads this warp issued land before the CTA's shared memory goes away
-        auto settle = [](uint32_t bar, uint32_t parity) {
-            for (uint32_t t = 0; t < (1u << 20) && !mbar_try_wait(bar, parity); ++t) {}
-        };
+        // a wait gave up somewhere: give the loads this warp issued a moment (100 us in all) to land before the CTA's
+        // shared memory goes away; a tile that was never issued cannot hold the CTA back
+        const uint64_t t_end = global_timer_ns() + 100000ull;
         for (uint32_t back = 1; back <= 2 * NSLOT && back <= pseq; ++back) {
             const uint32_t sq = pseq - back;
-            settle(smem_u32(&ctl->full[sq % NSLOT]), (sq / NSLOT) & 1);
+            while (!mbar_try_wait(smem_u32(&ctl->full[sq % NSLOT]), (sq / NSLOT) & 1) && global_timer_ns() < t_end) {}
         }
     }
     __syncwarp();
@@ -634,6 +664,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
+        if (lane == 0) dbg_stage(15);
     }
 }
 
@@ -655,7 +686,7 @@ struct AttnCall {
     AttnArgs a;
 };
 
-static int launch_attention(const AttnCall& c, bool fallback, cudaStream_t stream) {
+static int launch_attention(const AttnCall& c, int mode, cudaStream_t stream) {
     const AttnArgs& a = c.a;
     if (a.L <= 0 || a.H <= 0) return set_error(-1, "attention: L and H must be positive");
     if (((uintptr_t)c.q | (uintptr_t)c.k | (uintptr_t)c.v | (uintptr_t)a.out) & 15)
@@ -670,12 +701,12 @@ static int launch_attention(const AttnCall& c, bool fallback, cudaStream_t strea
     } else {
         tkm = tk; tvm = tv;
     }
-    static bool attr_set[2] = {false, false};
-    auto kern = fallback ? attention_kernel<true> : attention_kernel<false>;
-    if (!attr_set[fallback]) {
+    static bool attr_set[3] = {false, false, false};
+    auto kern = mode == 0 ? attention_kernel<0> : mode == 1 ? attention_kernel<1> : attention_kernel<2>;
+    if (!attr_set[mode]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ALLOC);
         if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
-        attr_set[fallback] = true;
+        attr_set[mode] = true;
     }
     kern<<<a.nq * a.H, NTHREADS, SMEM_ALLOC, stream>>>(tk, tv, tkm, tvm, a);
     cudaError_t e = cudaGetLastError();
@@ -714,7 +745,7 @@ extern "C" int es_block_attention(const void* q, const void* k, const void* v, v
     c.a.offset = offset; c.a.lse = lse; c.a.flags = flags; c.a.mass = mass;
     c.a.nvirt = 0; c.a.nref = 0;
     fill_q(c);
-    return launch_attention(c, false, (cudaStream_t)stream);
+    return launch_attention(c, 0, (cudaStream_t)stream);
 }
 
 extern "C" int es_sparse_attention(const void* q, const void* k, const void* v, const void* k_mean, const void* v_mean,
@@ -741,7 +772,7 @@ extern "C" int es_sparse_attention(const void* q, const void* k, const void* v, 
     c.a.k_rep = (const __nv_bfloat16*)k_rep; c.a.v_rep = (const __nv_bfloat16*)v_rep; c.a.log_counts = log_counts;
     c.a.nb4 = (c.a.nb + 1) * 4;
     fill_q(c);
-    return launch_attention(c, false, (cudaStream_t)stream);
+    return launch_attention(c, 0, (cudaStream_t)stream);
 }
 
 extern "C" int es_exact_fallback(const void* q, const void* k, const void* v, void* out, const int32_t* counts,
@@ -756,7 +787,23 @@ extern "C" int es_exact_fallback(const void* q, const void* k, const void* v, vo
     c.a.offset = lse; c.a.lse = lse; c.a.flags = const_cast<int32_t*>(flags); c.a.mass = nullptr;
     c.a.nvirt = 0; c.a.nref = 0;
     fill_q(c);
-    return launch_attention(c, true, (cudaStream_t)stream);
+    return launch_attention(c, 1, (cudaStream_t)stream);
+}
+
+extern "C" int es_compensate_fallback(const void* q, const void* k_mean, const void* v_mean, const uint8_t* keep,
+                                      float* lse, void* out, const int32_t* flags, int32_t L, int32_t H, void* stream) {
+    if (!q || !k_mean || !v_mean || !keep || !lse || !out || !flags)
+        return set_error(-1, "es_compensate_fallback: null pointer");
+    AttnCall c{};
+    // no exact blocks in this pass: the K / V maps are only placeholders and point at the mean tables
+    c.q = q; c.k = k_mean; c.v = v_mean; c.k_mean = k_mean; c.v_mean = v_mean;
+    fill_common(c.a, L, H, 0.f);
+    c.a.out = (__nv_bfloat16*)out; c.a.counts = nullptr; c.a.blocks = nullptr; c.a.nk = 0;
+    c.a.offset = lse; c.a.lse = lse; c.a.flags = const_cast<int32_t*>(flags); c.a.mass = nullptr;
+    c.a.keep = keep;
+    c.a.nvirt = (c.a.nb + 127) / 128; c.a.nref = 0;
+    fill_q(c);
+    return launch_attention(c, 2, (cudaStream_t)stream);
 }
 
 // Debugging aid: when `buffer` (device memory, es_debug_trace_words() 32-bit words, zeroed by the caller) is not NULL,
@@ -764,10 +811,12 @@ extern "C" int es_exact_fallback(const void* q, const void* k, const void* v, vo
 extern "C" int es_debug_set_trace(void* buffer) {
 #ifdef ES_TRACE
     es::g_trace = static_cast<uint32_t*>(buffer);
+    uint32_t* rep = buffer ? static_cast<uint32_t*>(buffer) + es::TRACE_CTAS * 2 * es::TRACE_ITERS * 8 : nullptr;
+    cudaMemcpyToSymbol(g_dbg_report, &rep, sizeof(rep));
     return 0;
 #else
     (void)buffer;
     return es::set_error(-4, "es_debug_set_trace: this build has no trace code (compile with -DES_TRACE)");
 #endif
 }
-extern "C" int es_debug_trace_words(void) { return es::TRACE_CTAS * 2 * es::TRACE_ITERS * 8; }
+extern "C" int es_debug_trace_words(void) { return es::TRACE_CTAS * 2 * es::TRACE_ITERS * 8 + 512; }

@@ -1,5 +1,5 @@
 // The memory-bound kernels around the attention kernel: block means, per-tile scales, mass estimates of the skipped
-// blocks, and the block-mean compensation of fallback tiles. Vectorised 16-byte loads, warp shuffles, mma.sync for the
+// blocks (the block-mean compensation of fallback tiles is a mode of the attention kernel). Vectorised 16-byte loads, warp shuffles, mma.sync for the
 // one small contraction (16 sampled query rows x block-mean keys).
 #include "es_api_internal.h"
 
@@ -190,84 +190,6 @@ estimate_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
     }
 }
 
-// ------------------------------------------------------------------------------------------------ compensation
-// Block-mean compensation of the skipped blocks for flagged tiles, in place (triton_ops.py:251-295):
-//   e_b = 2^min(c q.kmean_b - lse + log2 len_b, 100) over all blocks not kept;  out = (out + sum e v_b) / (1 + sum e);
-//   lse += log2(1 + sum e).  CTAs stride over the (tile, head) pairs; thread = row; the row's numerator lives in
-// shared memory with a padded stride so that the 128 rows hit distinct banks.
-constexpr int COMP_STRIDE = HD + 1;
-__global__ void __launch_bounds__(128)
-compensate_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ km,
-                  const __nv_bfloat16* __restrict__ vm, const uint8_t* __restrict__ keep, float* __restrict__ lse,
-                  __nv_bfloat16* __restrict__ out, const int* __restrict__ flags, float scale_log2, int L, int nb,
-                  float lb_last, int H, int nq) {
-    extern __shared__ float nu[];                    // [128][COMP_STRIDE]
-    const int tid = threadIdx.x;
-    for (int it = blockIdx.x; it < nq * H; it += gridDim.x) {
-        const int t = it / H, h = it % H;
-        if (flags[t * H + h] == 0) continue;
-        const int row = t * 128 + tid;
-        const bool rv = row < L;
-        uint32_t qr[64];
-        const __nv_bfloat16* qp = q + ((size_t)(rv ? row : 0) * H + h) * HD;
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const uint4 w = *reinterpret_cast<const uint4*>(qp + 8 * i);
-            qr[4 * i] = w.x; qr[4 * i + 1] = w.y; qr[4 * i + 2] = w.z; qr[4 * i + 3] = w.w;
-        }
-        float* mine = nu + tid * COMP_STRIDE;
-        for (int d = 0; d < HD; ++d) mine[d] = 0.f;
-        const float ls = lse[(size_t)row * H + h];
-        float lu = 0.f;
-        const uint8_t* kp = keep + ((size_t)h * nq + t) * nb;
-        for (int b = 0; b < nb; ++b) {
-            if (kp[b] != 0) continue;                // uniform over the CTA
-            const uint4* kr = reinterpret_cast<const uint4*>(km + ((size_t)b * H + h) * HD);
-            float s = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const uint4 w = __ldg(kr + i);
-                s = fmaf(bf16_lo(qr[4 * i]), bf16_lo(w.x), s); s = fmaf(bf16_hi(qr[4 * i]), bf16_hi(w.x), s);
-                s = fmaf(bf16_lo(qr[4 * i + 1]), bf16_lo(w.y), s); s = fmaf(bf16_hi(qr[4 * i + 1]), bf16_hi(w.y), s);
-                s = fmaf(bf16_lo(qr[4 * i + 2]), bf16_lo(w.z), s); s = fmaf(bf16_hi(qr[4 * i + 2]), bf16_hi(w.z), s);
-                s = fmaf(bf16_lo(qr[4 * i + 3]), bf16_lo(w.w), s); s = fmaf(bf16_hi(qr[4 * i + 3]), bf16_hi(w.w), s);
-            }
-            const float lb = (b == nb - 1) ? lb_last : 6.0f;
-            float e = exp2f(fminf(s * scale_log2 - ls + lb, 100.f));
-            e = rv ? e : 0.f;
-            lu += e;
-            const float eb = __bfloat162float(__float2bfloat16_rn(e));      // the reference rounds e to bf16 for e . v
-            const uint4* vr = reinterpret_cast<const uint4*>(vm + ((size_t)b * H + h) * HD);
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const uint4 w = __ldg(vr + i);
-                float* p = mine + 8 * i;
-                p[0] = fmaf(eb, bf16_lo(w.x), p[0]); p[1] = fmaf(eb, bf16_hi(w.x), p[1]);
-                p[2] = fmaf(eb, bf16_lo(w.y), p[2]); p[3] = fmaf(eb, bf16_hi(w.y), p[3]);
-                p[4] = fmaf(eb, bf16_lo(w.z), p[4]); p[5] = fmaf(eb, bf16_hi(w.z), p[5]);
-                p[6] = fmaf(eb, bf16_lo(w.w), p[6]); p[7] = fmaf(eb, bf16_hi(w.w), p[7]);
-            }
-        }
-        if (rv) {
-            __nv_bfloat16* op = out + ((size_t)row * H + h) * HD;
-            const float inv = 1.0f / (1.0f + lu);
-#pragma unroll 4
-            for (int i = 0; i < 16; ++i) {
-                uint4 w = *reinterpret_cast<const uint4*>(op + 8 * i);
-                const float* p = mine + 8 * i;
-                __nv_bfloat162 r0 = __floats2bfloat162_rn((bf16_lo(w.x) + p[0]) * inv, (bf16_hi(w.x) + p[1]) * inv);
-                __nv_bfloat162 r1 = __floats2bfloat162_rn((bf16_lo(w.y) + p[2]) * inv, (bf16_hi(w.y) + p[3]) * inv);
-                __nv_bfloat162 r2 = __floats2bfloat162_rn((bf16_lo(w.z) + p[4]) * inv, (bf16_hi(w.z) + p[5]) * inv);
-                __nv_bfloat162 r3 = __floats2bfloat162_rn((bf16_lo(w.w) + p[6]) * inv, (bf16_hi(w.w) + p[7]) * inv);
-                w.x = *reinterpret_cast<uint32_t*>(&r0); w.y = *reinterpret_cast<uint32_t*>(&r1);
-                w.z = *reinterpret_cast<uint32_t*>(&r2); w.w = *reinterpret_cast<uint32_t*>(&r3);
-                *reinterpret_cast<uint4*>(op + 8 * i) = w;
-            }
-        }
-        lse[(size_t)row * H + h] = rv ? ls + log2f(1.0f + lu) : 1e30f;
-    }
-}
-
 }  // namespace es
 
 using namespace es;
@@ -306,27 +228,5 @@ extern "C" int es_estimate_skipped(const void* q, const void* k_mean, const uint
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_mean, keep, offset, lse, mass, scale_exact, scale_skip,
         LOG2E_F / sqrtf((float)HD), L, nb, log2f((float)tail), H, nq);
     ES_CHECK_LAUNCH("estimate_skipped");
-    return 0;
-}
-
-extern "C" int es_compensate_fallback(const void* q, const void* k_mean, const void* v_mean, const uint8_t* keep,
-                                      float* lse, void* out, const int32_t* flags, int32_t L, int32_t H, void* stream) {
-    if (!q || !k_mean || !v_mean || !keep || !lse || !out || !flags)
-        return set_error(-1, "es_compensate_fallback: null pointer");
-    if (L <= 0 || H <= 0) return set_error(-1, "es_compensate_fallback: L and H must be positive");
-    const int nq = (L + 127) / 128, nb = (L + 63) / 64;
-    const int tail = L - (nb - 1) * 64;
-    const int smem = 128 * COMP_STRIDE * (int)sizeof(float);
-    static bool attr = false;
-    if (!attr) {
-        cudaError_t e = cudaFuncSetAttribute(compensate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
-        attr = true;
-    }
-    const int grid = nq * H < 1184 ? nq * H : 1184;
-    compensate_kernel<<<grid, 128, smem, (cudaStream_t)stream>>>(
-        (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_mean, (const __nv_bfloat16*)v_mean, keep, lse,
-        (__nv_bfloat16*)out, flags, LOG2E_F / sqrtf((float)HD), L, nb, log2f((float)tail), H, nq);
-    ES_CHECK_LAUNCH("compensate_fallback");
     return 0;
 }

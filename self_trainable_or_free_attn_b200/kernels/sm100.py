@@ -241,6 +241,17 @@ class Representatives:
 
     def build(self, q, k, v, k_mean=None, v_mean=None):
         """Representatives of every block; given k_mean / v_mean (nb, H, D), also the block means."""
+        t = _timer
+        if t is not None and "reps_build" in t.names:
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            self._build(q, k, v, k_mean, v_mean)
+            b.record()
+            t.events["reps_build"].append((a, b))
+        else:
+            self._build(q, k, v, k_mean, v_mean)
+
+    def _build(self, q, k, v, k_mean, v_mean):
         _cuda_bf16(q, k, v)
         assert q.shape == k.shape == v.shape == (self.L, self.H, self.D)
         lib = N.load()
