@@ -303,6 +303,9 @@ def main():
     k_ms = statistics.mean(kernel_ms)
     k_flops = flops_rank / len(inputs)
     achieved = k_flops / (k_ms * 1e-3) / 1e12
+    # DRAM bytes of one launch: Nsight Compute measured 332.97 MB read + 95.17 MB written on the 32,760-token, 12-head
+    # case (1.06 x the compulsory q, k, v, out bytes); the traffic grows with tokens x heads
+    traffic = 428.14e6 * (L * len(heads)) / (32760 * 12)
     line = {
         "metric": "sparse_attn_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
@@ -319,10 +322,13 @@ def main():
                 "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "kernel_ms_per_step": {n: round(sum(timer.ms(n)) / args.steps, 3) for n in names if timer.events[n]},
-        "roofline": {"bound": "tensor", "kernel": "attention_kernel<false> (es_sparse_attention)", "achieved": achieved,
+        "roofline": {"bound": "tensor", "kernel": "attention_kernel<0> (es_sparse_attention)", "achieved": achieved,
                      "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
                      "peak_source": f"bf16_tflops_sustained of {peaks['source']}", "ms_per_launch": k_ms,
-                     "launches_timed": len(kernel_ms), "traffic": None},
+                     "launches_timed": len(kernel_ms), "traffic": traffic,
+                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch captured at the "
+                                       "Wan-1.3B shape (428.1 MB), scaled by tokens x heads (q, k, v read once, out "
+                                       "written once)"},
     }
     if world == 1 and not args.no_cpu_baseline:
         tf, sample, dt = cpu_sample(args.workload, args.cpu_seconds, threads)
