@@ -26,3 +26,64 @@ def T(a, device="cpu"):
 def rel_l2(a, b):
     a, b = a.double(), b.double()
     return ((a - b).norm() / b.norm().clamp_min(1e-30)).item()
+
+
+# ---------------------------------------------------------------------------------------------- VSA2 golden cases
+# Inputs of tests/golden/vsa2.npz, rebuilt from numpy's legacy RandomState (a stable stream) on both sides.
+VSA_CASES = {   # name: (B, H, NB, seed, blk_cnt kind)
+    "fine": (1, 1, 5, 11, "mixed"),
+    "full": (1, 1, 5, 12, "tail"),
+    "route": (1, 2, 12, 13, "mixed"),
+    "tiers": (1, 1, 5, 14, "mixed"),
+}
+
+
+def vsa_counts(nb, kind, rs):
+    c = np.full(nb, 64, dtype=np.int32)
+    if kind == "tail":
+        c[-1] = 37
+    elif kind == "mixed":
+        c = rs.randint(1, 65, size=nb).astype(np.int32)
+        c[0] = 64
+        if nb > 2:
+            c[1] = 1
+    return torch.from_numpy(c)
+
+
+def vsa_case(name, D=128, dtype=torch.bfloat16):
+    """(q, k, v, gate, blk_cnt, dout): q, k, v [B,H,NB*64,D] with zeroed padding slots, gate [B,H,L], dout like q."""
+    B, H, nb, seed, kind = VSA_CASES[name]
+    rs = np.random.RandomState(seed)
+    cnt = vsa_counts(nb, kind, rs)
+    L = nb * 64
+    pos = np.arange(L)
+    valid = torch.from_numpy((pos % 64) < cnt.numpy()[pos // 64])[None, None, :, None]
+    mk = lambda: (torch.from_numpy(rs.standard_normal((B, H, L, D)).astype(np.float32)) * valid).to(dtype).contiguous()
+    q, k, v = mk(), mk(), mk()
+    gate = torch.from_numpy((rs.standard_normal((B, H, L)) * 1.5).astype(np.float32)).to(dtype)
+    dout = (torch.from_numpy(rs.standard_normal((B, H, L, D)).astype(np.float32)) * valid).to(dtype)
+    return q, k, v, gate, cnt, dout
+
+
+def vsa_mask(name, nb):
+    """Frozen block mask [B,H,NB,NB]: 30 % random, a query block without edges, one that sees everything, a single edge."""
+    B, H, _, seed, _ = VSA_CASES[name]
+    rs = np.random.RandomState(seed + 100)
+    m = torch.from_numpy(rs.random_sample((B, H, nb, nb)) < 0.3)
+    m[:, :, 0] = False
+    m[:, :, -1] = True
+    if nb > 3:
+        m[:, :, 2] = False
+        m[:, :, 2, 1] = True
+    return m
+
+
+def vsa_tiers(nb):
+    """Tier masks (tier A, tier A or B) [1,1,NB,NB]: A 25 %, B a further 35 %; row 0 has no tier A, row 1 is all tier C."""
+    rs = np.random.RandomState(77)
+    u = torch.from_numpy(rs.random_sample((1, 1, nb, nb)))
+    a, ab = u < 0.25, u < 0.6
+    a[:, :, 0] = False
+    a[:, :, 1] = False
+    ab[:, :, 1] = False
+    return a, ab
