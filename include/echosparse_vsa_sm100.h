@@ -1,0 +1,94 @@
+/* C ABI of the VSA2 part of libechosparse_sm100.so (B200, sm_100a): the stages behind `echosparse.vsa`.
+ *
+ * Conventions (all entry points):
+ *   - plain device pointers and sizes; the caller allocates every buffer (the reference's extension allocates its outputs
+ *     with torch::empty; here the Python layer above this ABI does); `stream` is a cudaStream_t; nothing synchronises;
+ *   - return 0 on success, a negative code on a rejected call or a failed launch; es_last_error() gives the text;
+ *   - token tensors are [BH, L, D] contiguous, L = NB * 64, D = 64 or 128, dtype 0 = bf16, 1 = fp16;
+ *     blk_cnt [NB] int32 = valid tokens per 64-token block (1..64, valid tokens first); padded slots output 0;
+ *   - CSR block lists: ptr [BH * (NB + 1)] int32 absolute offsets into idx, ids ascending per row;
+ *   - lse [BH, L] fp32 is the natural-log LSE over the selected keys, -inf for rows without a key and for padded rows.
+ * Each declaration names the launcher / binding of the reference (shaoshitong/self_trainable_or_free_attn) it replaces.
+ */
+#ifndef ECHOSPARSE_VSA_SM100_H
+#define ECHOSPARSE_VSA_SM100_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Group means of the R-token router groups (qr, kr, optionally vr: [BH, Lr_pad, D], row = block * (64 / R) + group) and
+ * block means (qc, kc, vc: [BH, NBc_pad, D]) over the valid tokens, rounded once to the element type; padding rows zero.
+ * Any output pointer may be NULL. Replaces `pool_fwd` (csrc/vsa/vsa2_api.cpp:904, launch_pool csrc/vsa/vsa2_kernels.h:193). */
+int es_vsa_pool(const void* q, const void* k, const void* v, void* qr, void* kr, void* vr, void* qc, void* kc, void* vc,
+                const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D, int32_t R, int32_t Lr_pad, int32_t NBc_pad,
+                int32_t dtype, void* stream);
+
+/* log2-domain LSE of every pooled query row over all valid pooled keys: lse2 [BH, Lr_pad].
+ * Replaces `router_lse` (launch_router_lse, csrc/vsa/vsa2_kernels.h:208). */
+int es_vsa_router_lse(const void* qr, const void* kr, float* lse2, const int32_t* blk_cnt, int32_t BH, int32_t NB, int32_t D,
+                      int32_t R, int32_t Lr_pad, int32_t dtype, void* stream);
+
+/* Block scores [bh_count, NB, NB] fp32 of the heads bh0 .. bh0 + bh_count - 1: the pooled softmax summed over the group
+ * pairs of a block pair; row_norm 1 divides by (64 / R)^2, 0 by the query block's number of valid groups.
+ * Replaces `router_scores` (launch_router_scores, csrc/vsa/vsa2_kernels.h:209). */
+int es_vsa_router_scores(const void* qr, const void* kr, const float* lse2, float* scores, const int32_t* blk_cnt, int32_t BH,
+                         int32_t NB, int32_t D, int32_t R, int32_t Lr_pad, int32_t bh0, int32_t bh_count, int32_t row_norm,
+                         int32_t dtype, void* stream);
+
+/* Bytes of scratch es_vsa_global_topk needs. Replaces topk_workspace_bytes (csrc/vsa/vsa2_kernels.h:222). */
+long long es_vsa_topk_workspace_bytes(int32_t bh_count, int32_t NB);
+
+/* Exact global selection: the `budget` largest scores of every (b, h) in the order (score descending, flat index
+ * ascending), as q -> kv lists and their inverse. ptr arrays [BH * (NB + 1)] (rows of heads bh0 .. are written), idx arrays
+ * [BH * budget]; head bh owns idx[bh * budget, (bh + 1) * budget). Replaces `global_topk_into` / `route`
+ * (launch_global_topk, csrc/vsa/vsa2_kernels.h:238). */
+int es_vsa_global_topk(const float* scores, int32_t NB, int32_t bh0, int32_t bh_count, long long budget, int32_t* q2k_ptr,
+                       int32_t* q2k_idx, int32_t* k2q_ptr, int32_t* k2q_idx, void* workspace, void* stream);
+
+/* Attention of every 64-row query block over the valid tokens of its listed kv blocks (online softmax): o [BH, L, D],
+ * lse [BH, L]. Also the coarse branch (block means as a sequence, 64-row tiles with their own counts, dense lists).
+ * Replaces `attn_fwd` (launch_attn_fwd, csrc/vsa/vsa2_kernels.h:146). */
+int es_vsa_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* q2k_ptr,
+                    const int32_t* q2k_idx, const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D, int32_t dtype,
+                    void* stream);
+
+/* dK, dV of the same attention from the kv -> q lists, one owner per kv block (no atomics). Outputs in the element type
+ * (dk, dv) or fp32 (dk_f32, dv_f32, used instead when not NULL); add_dk / add_dv [BH, add_nb, D] fp32 are optional per-block
+ * gradients added as add / count to every valid token (the unpooling of the coarse branch). delta [BH, L] = rowsum(dO * O).
+ * Replaces the dK / dV part of `attn_bwd` (launch_attn_bwd, csrc/vsa/vsa2_kernels.h:151). */
+int es_vsa_attn_bwd_kv(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
+                       void* dk, void* dv, float* dk_f32, float* dv_f32, const float* add_dk, const float* add_dv,
+                       int32_t add_nb, const int32_t* k2q_ptr, const int32_t* k2q_idx, const int32_t* blk_cnt, int32_t BH,
+                       int32_t L, int32_t D, int32_t dtype, void* stream);
+
+/* dQ from the q -> kv lists, one owner per query block (no atomics); same output and add conventions.
+ * Replaces `attn_bwd_q` (launch_attn_bwd_q, csrc/vsa/vsa2_kernels.h:177). */
+int es_vsa_attn_bwd_q(const void* q, const void* k, const void* v, const void* dout, const float* lse, const float* delta,
+                      void* dq, float* dq_f32, const float* add_dq, int32_t add_nb, const int32_t* q2k_ptr,
+                      const int32_t* q2k_idx, const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D, int32_t dtype,
+                      void* stream);
+
+/* o = valid ? o_f + w * o_c[block] : 0 with w = act(gate); gate_mode 0 none (w = 1), 1 per token [BH, L], 2 per element
+ * [BH, L, D]; gate_act 0 tanh, 1 identity. Replaces `fuse_fwd` (launch_fuse_fwd, csrc/vsa/vsa2_kernels.h:279). */
+int es_vsa_fuse_fwd(const void* of, const void* oc, const void* gate, void* o, const int32_t* blk_cnt, int32_t BH, int32_t L,
+                    int32_t D, int32_t NBc_pad, int32_t gate_mode, int32_t gate_act, int32_t dtype, void* stream);
+
+/* Backward of the fusion: dout_f (dO on valid rows, 0 elsewhere; may be NULL), delta_f [BH, L] = rowsum(dO * o_f),
+ * dout_c [BH, NBc_pad, D] = sum over the block's valid rows of w * dO (rows >= NB are left to the caller),
+ * delta_c [BH, NBc_pad] = rowsum(dout_c * o_c), dgate like gate. Replaces `fuse_bwd` (csrc/vsa/vsa2_kernels.h:295). */
+int es_vsa_fuse_bwd(const void* dout, const void* of, const void* oc, const void* gate, void* dout_f, float* delta_f,
+                    void* dout_c, float* delta_c, void* dgate, const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D,
+                    int32_t NBc_pad, int32_t gate_mode, int32_t gate_act, int32_t dtype, void* stream);
+
+/* out = valid ? acc + add[block] / count : 0 in the element type (acc [BH, L, D] fp32 and add [BH, add_nb, D] fp32 may each
+ * be NULL). Replaces `finalize` (launch_finalize, csrc/vsa/vsa2_kernels.h:306). */
+int es_vsa_finalize(const float* acc, const float* add, void* out, const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D,
+                    int32_t add_nb, int32_t dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,4 +1,5 @@
-"""ctypes binding of libechosparse_sm100.so (the C ABI declared in include/echosparse_sm100.h).
+"""ctypes binding of libechosparse_sm100.so (the C ABI declared in include/echosparse_sm100.h and
+include/echosparse_vsa_sm100.h).
 
 There is no fallback: if the library is missing or a call fails, this raises. PyTorch tensors are passed as raw device
 pointers; the launch goes on torch's current CUDA stream.
@@ -36,10 +37,22 @@ SIGNATURES = {
     "es_reps_kmeans": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     "es_reps_metric_static": [_P, _P, _P, _P, _I, _I, _P],
     "es_reps_metric_static_max_heads": [],
+    "es_vsa_pool": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "es_vsa_router_lse": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    "es_vsa_router_scores": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "es_vsa_topk_workspace_bytes": [_I, _I],
+    "es_vsa_global_topk": [_P, _I, _I, _I, ctypes.c_longlong, _P, _P, _P, _P, _P, _P],
+    "es_vsa_attn_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _P],
+    "es_vsa_attn_bwd_kv": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "es_vsa_attn_bwd_q": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "es_vsa_fuse_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "es_vsa_fuse_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "es_vsa_finalize": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
     "es_debug_set_trace": [_P],
     "es_debug_trace_words": [],
 }
-_RESTYPES = {"es_last_error": ctypes.c_char_p, "es_launch_count": ctypes.c_longlong}
+_RESTYPES = {"es_last_error": ctypes.c_char_p, "es_launch_count": ctypes.c_longlong,
+             "es_vsa_topk_workspace_bytes": ctypes.c_longlong}
 
 _lib = None
 

@@ -1,0 +1,315 @@
+"""VSA2 operator: autograd wiring around the native kernels (C ABI of include/echosparse_vsa_sm100.h).
+
+Mirrors the public entry points of the reference's `echosparse/vsa/ops.py`: `Selection` (:90-117), `mask_to_selection`
+(:107-122), `route` (:216-223), `vsa2_attention` (:534-571) and `fine_block_sparse_attention` (:670-679), with the same
+argument meaning, layout contract and error behaviour:
+
+  q, k, v : [B, H, L, D] contiguous, bf16 or fp16, D in {64, 128}, L = NB * 64, tokens block-major, block i holding
+            blk_cnt[i] valid tokens first, then padding (finite values; zeros recommended).
+  gate    : optional pre-activation, [B, H, L] or [B, H, L, D]. O = O_fine + act(gate) * O_coarse[block].
+  blk_cnt : int32 [NB], 1..64.
+
+Every stage is a CUDA kernel of this library; torch is used for allocation and for the shape-only dense CSR of the coarse
+branch. The backward has one owner per output row in both passes (kv -> q lists for dK / dV, q -> kv lists for dQ), so
+gradients are reproducible bit for bit; the intermediates are released after the first backward (ops.py:520-522 there).
+"""
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from .. import _native as N
+
+GATE_ACTS = {"tanh": 0, "identity": 1}
+ROW_NORMS = {"valid_groups": 0, "paper": 1}
+_DTYPES = {torch.bfloat16: 0, torch.float16: 1}
+
+
+@dataclass
+class Selection:
+    """Exact block selection, CSR. Absolute offsets into the idx arrays."""
+    q2k_ptr: torch.Tensor   # [B, H, NB+1] int32
+    q2k_idx: torch.Tensor   # [nnz] int32, kv block ids ascending per row
+    k2q_ptr: torch.Tensor   # [B, H, NB+1]
+    k2q_idx: torch.Tensor   # [nnz], query block ids ascending per column
+
+    def row_counts(self):
+        return (self.q2k_ptr[..., 1:] - self.q2k_ptr[..., :-1]).to(torch.int64)
+
+    def to_mask(self, nb):
+        """Dense bool block mask [B, H, NB, NB]."""
+        B, H = self.q2k_ptr.shape[:2]
+        ptr = self.q2k_ptr.reshape(B * H, nb + 1).to(torch.int64)
+        mask = torch.zeros(B * H * nb, nb, dtype=torch.bool, device=ptr.device)
+        cnt = (ptr[:, 1:] - ptr[:, :-1]).reshape(-1)
+        rows = torch.repeat_interleave(torch.arange(B * H * nb, device=ptr.device), cnt)
+        # rows of one (b, h) are contiguous in idx; different (b, h) may leave gaps between their ranges
+        offs = torch.arange(int(cnt.sum()), device=ptr.device) - torch.repeat_interleave(torch.cumsum(cnt, 0) - cnt, cnt)
+        src = torch.repeat_interleave(ptr[:, :-1].reshape(-1), cnt) + offs
+        mask[rows, self.q2k_idx[src].to(torch.int64)] = True
+        return mask.reshape(B, H, nb, nb)
+
+
+def mask_to_selection(mask):
+    """Bool block mask [B, H, NB, NB] -> CSR selection (test / diagnostic utility)."""
+    assert mask.dim() == 4 and mask.dtype == torch.bool
+
+    def csr(m):
+        B, H, n, _ = m.shape
+        cnt = m.reshape(-1, n).sum(-1).to(torch.int64)
+        incl = torch.cumsum(cnt, 0)
+        ptr = torch.cat([(incl - cnt).reshape(B * H, n), incl.reshape(B * H, n)[:, -1:]], dim=1)
+        idx = m.reshape(-1, n).nonzero()[:, 1]
+        if idx.numel() == 0:
+            idx = torch.zeros(1, dtype=torch.int64, device=m.device)
+        return ptr.reshape(B, H, n + 1).to(torch.int32).contiguous(), idx.to(torch.int32).contiguous()
+
+    qp, qi = csr(mask)
+    kp, ki = csr(mask.transpose(-1, -2).contiguous())
+    return Selection(qp, qi, kp, ki)
+
+
+def _check_tokens(q, k, v):
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        if not t.is_cuda:
+            raise RuntimeError(f"{name} must be a CUDA tensor: this operator has no CPU path")
+        if not t.is_contiguous():
+            raise ValueError(f"{name} must be contiguous [B,H,L,D]")
+    if q.dtype not in _DTYPES or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise RuntimeError("q, k, v must share the dtype bfloat16 or float16")
+    B, H, L, D = q.shape
+    if k.shape != q.shape or v.shape != q.shape or L % 64 != 0 or D not in (64, 128):
+        raise RuntimeError("q, k, v must be [B, H, NB*64, D] with D in {64, 128}")
+    return B, H, L, D
+
+
+def _pad64(n):
+    return -(-n // 64) * 64
+
+
+def pool_fwd(q, k, v, blk_cnt, R):
+    """(qr, kr [B,H,Lr_pad,D] router group means; qc, kc, vc [B,H,NBc_pad,D] block means)."""
+    B, H, L, D = q.shape
+    nb, G = L // 64, 64 // R
+    lr_pad, nbc_pad = _pad64(nb * G), _pad64(nb)
+    mk = lambda n: torch.empty(B, H, n, D, device=q.device, dtype=q.dtype)
+    qr, kr, qc, kc, vc = mk(lr_pad), mk(lr_pad), mk(nbc_pad), mk(nbc_pad), mk(nbc_pad)
+    N.check(N.load().es_vsa_pool(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(qr), N.ptr(kr), None, N.ptr(qc), N.ptr(kc), N.ptr(vc),
+                                 N.ptr(blk_cnt), B * H, L, D, R, lr_pad, nbc_pad, _DTYPES[q.dtype], N.stream_ptr()),
+            "es_vsa_pool")
+    return qr, kr, qc, kc, vc
+
+
+def router_scores(qr, kr, blk_cnt, R, row_norm=1):
+    """Block scores [B, H, NB, NB] fp32 of the PSP router (diagnostic; `route` uses the same kernels)."""
+    B, H, lr_pad, D = qr.shape
+    nb = blk_cnt.numel()
+    lse2 = torch.empty(B, H, lr_pad, device=qr.device, dtype=torch.float32)
+    lib, dt, st = N.load(), _DTYPES[qr.dtype], N.stream_ptr()
+    N.check(lib.es_vsa_router_lse(N.ptr(qr), N.ptr(kr), N.ptr(lse2), N.ptr(blk_cnt), B * H, nb, D, R, lr_pad, dt, st),
+            "es_vsa_router_lse")
+    scores = torch.empty(B, H, nb, nb, device=qr.device, dtype=torch.float32)
+    N.check(lib.es_vsa_router_scores(N.ptr(qr), N.ptr(kr), N.ptr(lse2), N.ptr(scores), N.ptr(blk_cnt), B * H, nb, D, R,
+                                     lr_pad, 0, B * H, row_norm, dt, st), "es_vsa_router_scores")
+    return scores
+
+
+def global_topk(scores, budget):
+    """Exact global top-`budget` of every (b, h) score matrix -> Selection."""
+    B, H, nb, _ = scores.shape
+    budget = max(0, min(int(budget), nb * nb))
+    dev = scores.device
+    lib = N.load()
+    i32 = dict(device=dev, dtype=torch.int32)
+    qp, kp = torch.empty(B, H, nb + 1, **i32), torch.empty(B, H, nb + 1, **i32)
+    qi, ki = torch.empty(max(1, B * H * budget), **i32), torch.empty(max(1, B * H * budget), **i32)
+    ws = torch.empty(int(lib.es_vsa_topk_workspace_bytes(B * H, nb)), device=dev, dtype=torch.uint8)
+    N.check(lib.es_vsa_global_topk(N.ptr(scores.contiguous()), nb, 0, B * H, budget, N.ptr(qp), N.ptr(qi), N.ptr(kp),
+                                   N.ptr(ki), N.ptr(ws), N.stream_ptr()), "es_vsa_global_topk")
+    return Selection(qp, qi, kp, ki)
+
+
+def budget_from_topk(nb, topk, budget):
+    if budget is not None:
+        return int(budget)
+    if topk is None:
+        raise ValueError("pass topk (average kv blocks per query block) or budget")
+    return int(nb) * int(topk)
+
+
+def _route(qr, kr, blk_cnt, R, budget, row_norm):
+    return global_topk(router_scores(qr, kr, blk_cnt, R, row_norm), budget)
+
+
+def route(q, k, blk_cnt, R=16, topk=None, budget=None, row_norm="paper"):
+    """Standalone VSA2 PSP router + exact global top-k (stop-gradient)."""
+    _check_tokens(q, k, k)
+    blk_cnt = blk_cnt.to(torch.int32).contiguous()
+    qr, kr, _, _, _ = pool_fwd(q, k, k, blk_cnt, R)
+    return _route(qr, kr, blk_cnt, R, budget_from_topk(q.shape[2] // 64, topk, budget), ROW_NORMS[row_norm])
+
+
+def attn_fwd(q, k, v, ptr, idx, cnt):
+    """(O, lse) of the list attention; q, k, v [B, H, L, D], lists over L / 64 blocks."""
+    B, H, L, D = q.shape
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, L, device=q.device, dtype=torch.float32)
+    N.check(N.load().es_vsa_attn_fwd(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(o), N.ptr(lse), N.ptr(ptr), N.ptr(idx),
+                                     N.ptr(cnt), B * H, L, D, _DTYPES[q.dtype], N.stream_ptr()), "es_vsa_attn_fwd")
+    return o, lse
+
+
+def _coarse_meta(B, H, nb, nbc_pad, device):
+    """Dense CSR over the 64-row tiles of the pooled sequence (shape-only metadata) and the tiles' valid counts."""
+    T = nbc_pad // 64
+    cnt = torch.clamp(nb - 64 * torch.arange(T, device=device), max=64).to(torch.int32).contiguous()
+    bh = torch.arange(B * H, device=device, dtype=torch.int64)
+    ptr = (bh[:, None] * (T * T) + torch.arange(T + 1, device=device, dtype=torch.int64)[None, :] * T)
+    idx = torch.arange(T, device=device, dtype=torch.int32).repeat(B * H * T).contiguous()
+    return cnt, ptr.to(torch.int32).reshape(B, H, T + 1).contiguous(), idx
+
+
+def _bwd_kv(q, k, v, dout, lse, delta, ptr, idx, cnt, add_dk=None, add_dv=None, f32=False):
+    B, H, L, D = q.shape
+    mk = (lambda: torch.empty(B, H, L, D, device=q.device, dtype=torch.float32)) if f32 else (lambda: torch.empty_like(q))
+    dk, dv = mk(), mk()
+    add_nb = add_dk.shape[2] if add_dk is not None else 0
+    N.check(N.load().es_vsa_attn_bwd_kv(
+        N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(dout), N.ptr(lse), N.ptr(delta), None if f32 else N.ptr(dk),
+        None if f32 else N.ptr(dv), N.ptr(dk) if f32 else None, N.ptr(dv) if f32 else None, N.ptr(add_dk), N.ptr(add_dv),
+        add_nb, N.ptr(ptr), N.ptr(idx), N.ptr(cnt), B * H, L, D, _DTYPES[q.dtype], N.stream_ptr()), "es_vsa_attn_bwd_kv")
+    return dk, dv
+
+
+def _bwd_q(q, k, v, dout, lse, delta, ptr, idx, cnt, add_dq=None, f32=False):
+    B, H, L, D = q.shape
+    dq = torch.empty(B, H, L, D, device=q.device, dtype=torch.float32) if f32 else torch.empty_like(q)
+    add_nb = add_dq.shape[2] if add_dq is not None else 0
+    N.check(N.load().es_vsa_attn_bwd_q(
+        N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(dout), N.ptr(lse), N.ptr(delta), None if f32 else N.ptr(dq),
+        N.ptr(dq) if f32 else None, N.ptr(add_dq), add_nb, N.ptr(ptr), N.ptr(idx), N.ptr(cnt), B * H, L, D,
+        _DTYPES[q.dtype], N.stream_ptr()), "es_vsa_attn_bwd_q")
+    return dq
+
+
+def _gate_mode(gate, q):
+    if gate is None:
+        return 0
+    if gate.shape == q.shape[:3]:
+        return 1
+    if gate.shape == q.shape:
+        return 2
+    raise RuntimeError("gate must be [B, H, L] or [B, H, L, D]")
+
+
+def _fuse_bwd(dout, of, oc, gate, blk_cnt, gate_act):
+    B, H, L, D = dout.shape
+    nbc_pad = oc.shape[2]
+    mode = _gate_mode(gate, dout)
+    delta_f = torch.empty(B, H, L, device=dout.device, dtype=torch.float32)
+    dout_c = torch.zeros_like(oc)
+    delta_c = torch.zeros(B, H, nbc_pad, device=dout.device, dtype=torch.float32)
+    dgate = torch.empty_like(gate) if gate is not None else None
+    N.check(N.load().es_vsa_fuse_bwd(N.ptr(dout), N.ptr(of), N.ptr(oc), N.ptr(gate), None, N.ptr(delta_f), N.ptr(dout_c),
+                                     N.ptr(delta_c), N.ptr(dgate), N.ptr(blk_cnt), B * H, L, D, nbc_pad, mode, gate_act,
+                                     _DTYPES[dout.dtype], N.stream_ptr()), "es_vsa_fuse_bwd")
+    return delta_f, dout_c, delta_c, dgate
+
+
+class _Function(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, gate, blk_cnt, R, budget, row_norm, gate_act, sel_in):
+        B, H, L, D = q.shape
+        nb = L // 64
+        qr, kr, qc, kc, vc = pool_fwd(q, k, v, blk_cnt, R)
+        c_cnt, c_ptr, c_idx = _coarse_meta(B, H, nb, qc.shape[2], q.device)
+        oc, lse_c = attn_fwd(qc, kc, vc, c_ptr, c_idx, c_cnt)
+        sel = sel_in if sel_in is not None else _route(qr, kr, blk_cnt, R, budget, row_norm)
+        of, lse_f = attn_fwd(q, k, v, sel.q2k_ptr, sel.q2k_idx, blk_cnt)
+        o = torch.empty_like(q)
+        N.check(N.load().es_vsa_fuse_fwd(N.ptr(of), N.ptr(oc), N.ptr(gate), N.ptr(o), N.ptr(blk_cnt), B * H, L, D,
+                                         oc.shape[2], _gate_mode(gate, q), gate_act, _DTYPES[q.dtype], N.stream_ptr()),
+                "es_vsa_fuse_fwd")
+        ctx.save_for_backward(q, k, v, gate, blk_cnt)
+        # held as attributes, not saved tensors, so that backward can release them after their last use
+        ctx.inter = [qc, kc, vc, oc, lse_c, of, lse_f, sel, c_cnt, c_ptr, c_idx]
+        ctx.has_gate = gate is not None
+        ctx.gate_act = gate_act
+        ctx.mark_non_differentiable(sel.q2k_ptr, sel.q2k_idx, sel.k2q_ptr, sel.k2q_idx)
+        return o, sel.q2k_ptr, sel.q2k_idx, sel.k2q_ptr, sel.k2q_idx
+
+    @staticmethod
+    def backward(ctx, dout, *unused):
+        q, k, v, gate, blk_cnt = ctx.saved_tensors
+        if ctx.inter is None:
+            raise RuntimeError("VSA backward frees its intermediates after the first backward; "
+                               "re-run the forward instead of backward(retain_graph=True) twice")
+        qc, kc, vc, oc, lse_c, of, lse_f, sel, c_cnt, c_ptr, c_idx = ctx.inter
+        dout = dout.contiguous()
+        delta_f, dout_c, delta_c, dgate = _fuse_bwd(dout, of, oc, gate if ctx.has_gate else None, blk_cnt, ctx.gate_act)
+        ctx.inter[5] = None
+        del of
+        # coarse branch (dense over the block means) -> fp32 per-block gradients; the dense lists are their own inverse
+        dkc, dvc = _bwd_kv(qc, kc, vc, dout_c, lse_c, delta_c, c_ptr, c_idx, c_cnt, f32=True)
+        dqc = _bwd_q(qc, kc, vc, dout_c, lse_c, delta_c, c_ptr, c_idx, c_cnt, f32=True)
+        # fine branch on the forward's selection, plus the unpooled coarse gradients (block gradient / count per token)
+        dk, dv = _bwd_kv(q, k, v, dout, lse_f, delta_f, sel.k2q_ptr, sel.k2q_idx, blk_cnt, add_dk=dkc, add_dv=dvc)
+        dq = _bwd_q(q, k, v, dout, lse_f, delta_f, sel.q2k_ptr, sel.q2k_idx, blk_cnt, add_dq=dqc)
+        ctx.inter = None
+        return (dq, dk, dv, dgate if ctx.has_gate else None) + (None,) * 6
+
+
+def vsa2_attention(q, k, v, gate, blk_cnt, *, R=16, topk=None, budget=None, row_norm="paper", gate_act="tanh",
+                   backend="auto", selection: Optional[Selection] = None, return_selection=False):
+    """Full VSA2 attention: O = O_fine + act(gate) * repeat(O_coarse).
+
+    The router (pool R -> softmax over all pooled keys -> pool to 64-token blocks) and the exact global top-k (budget =
+    NB * topk connections per (b, h)) run on every call unless a frozen `selection` is passed (testing). `backend` is kept
+    for signature compatibility; there is a single sm_100a backend.
+    """
+    if backend not in ("auto", "generic"):
+        raise ValueError(f"unknown backend {backend!r}: this build has the one sm_100a backend ('auto' or 'generic')")
+    _check_tokens(q, k, v)
+    nb = q.shape[2] // 64
+    blk_cnt = blk_cnt.to(torch.int32).contiguous()
+    if blk_cnt.numel() != nb:
+        raise RuntimeError("blk_cnt must have one entry per 64-token block")
+    if gate is not None:
+        gate = gate.contiguous()
+        if gate.dtype != q.dtype:
+            raise RuntimeError("gate must have the dtype of q")
+        _gate_mode(gate, q)
+    b = budget_from_topk(nb, topk, budget) if selection is None else 0
+    o, qp, qi, kp, ki = _Function.apply(q, k, v, gate, blk_cnt, int(R), b, ROW_NORMS[row_norm], GATE_ACTS[gate_act],
+                                        selection)
+    if return_selection:
+        return o, Selection(qp, qi, kp, ki)
+    return o
+
+
+class _FineFunction(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, blk_cnt, sel):
+        of, lse = attn_fwd(q, k, v, sel.q2k_ptr, sel.q2k_idx, blk_cnt)
+        ctx.save_for_backward(q, k, v, blk_cnt, of, lse, sel.q2k_ptr, sel.q2k_idx, sel.k2q_ptr, sel.k2q_idx)
+        ctx.mark_non_differentiable(lse)
+        return of, lse
+
+    @staticmethod
+    def backward(ctx, dout, dlse):
+        q, k, v, blk_cnt, of, lse, qp, qi, kp, ki = ctx.saved_tensors
+        B, H, L, D = q.shape
+        dout = dout.contiguous()
+        oc0 = torch.zeros(B, H, _pad64(L // 64), D, device=q.device, dtype=q.dtype)
+        delta_f, _, _, _ = _fuse_bwd(dout, of, oc0, None, blk_cnt, 0)
+        dk, dv = _bwd_kv(q, k, v, dout, lse, delta_f, kp, ki, blk_cnt)
+        dq = _bwd_q(q, k, v, dout, lse, delta_f, qp, qi, blk_cnt)
+        return dq, dk, dv, None, None
+
+
+def fine_block_sparse_attention(q, k, v, blk_cnt, selection: Selection, backend="auto"):
+    """Diagnostic fine-only primitive (no coarse branch, no router). Returns (O_f, lse); query blocks without an edge and
+    padded rows give O_f = 0 and lse = -inf."""
+    _check_tokens(q, k, v)
+    return _FineFunction.apply(q, k, v, blk_cnt.to(torch.int32).contiguous(), selection)

@@ -1,5 +1,5 @@
-"""The C-ABI library loads and exports every symbol that include/echosparse_sm100.h declares. No GPU needed: nothing
-is launched."""
+"""The C-ABI library loads and exports every symbol that the headers under include/ declare. No GPU needed: nothing is
+launched."""
 import ctypes
 import os
 import re
@@ -8,7 +8,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "echosparse_sm100.h")).read()
+    inc = os.path.join(ROOT, "include")
+    text = "".join(open(os.path.join(inc, f)).read() for f in sorted(os.listdir(inc)) if f.endswith(".h"))
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     return sorted(set(re.findall(r"\b(es_[a-z0-9_]+)\s*\(", text)))
 
