@@ -88,6 +88,52 @@ int es_vsa_fuse_bwd(const void* dout, const void* of, const void* oc, const void
 int es_vsa_finalize(const float* acc, const float* add, void* out, const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D,
                     int32_t add_nb, int32_t dtype, void* stream);
 
+/* ---- split-KV scheduling (balanced chunk tasks for long lists) ----
+ * Plan of one CSR list ptr [BH * (NB + 1)] (q -> kv for the forward and the dQ pass, kv -> q for the dK / dV pass). A row of n
+ * blocks is eligible when n >= max(min_len, ceil(tail_frac * W / resident), ceil(rel_mean * edges of its (b, h) / NB)) (W = all
+ * edges; min_len >= chunk + 1; rel_mean = tail_frac = 0 switch those terms off); eligible rows have ceil(n / chunk) balanced
+ * chunks; nothing splits when more than `budget` rows are eligible; rows split while the running chunk count of the eligible
+ * rows stays <= max_slots. tasks [(BH * NB + max_slots), 4] = {row, first edge, end edge, slot} (split chunks first, slot =
+ * task index, then one direct task with slot -1 per other row); merges [max(1, min(BH * NB, max_slots / 2)), 4] = {row, first
+ * slot, chunks, 0}; info [8] = tasks, split rows, split slots, rows, eligible rows, eligible <= budget, threshold without the
+ * per-head term, W. All counts stay on the device. Replaces `split_plan` (csrc/vsa/vsa2_api.cpp:464-520, csrc/vsa/split.cu:33-110). */
+long long es_vsa_split_plan_workspace_bytes(int32_t BH, int32_t NB);
+int es_vsa_split_plan(const int32_t* ptr, int32_t BH, int32_t NB, int32_t chunk, int32_t max_slots, int32_t min_len,
+                      double rel_mean, double tail_frac, int32_t resident, int32_t budget, int32_t* tasks, int32_t* merges,
+                      int32_t* info, void* workspace, void* stream);
+
+/* es_vsa_attn_fwd over a task list (grid of n_tasks_cap CTAs; those past info[0] exit): direct tasks write o / lse, chunk
+ * tasks write fp32 normalised partials part_o [slots, 64, D] and their log2-domain lse part_lse [slots, 64].
+ * Replaces `attn_fwd_tasks` (csrc/vsa/vsa2_api.cpp:522-570). */
+int es_vsa_attn_fwd_tasks(const void* q, const void* k, const void* v, void* o, float* lse, const int32_t* q2k_idx,
+                          const int32_t* blk_cnt, const int32_t* tasks, const int32_t* task_info, int32_t n_tasks_cap,
+                          float* part_o, float* part_lse, int32_t BH, int32_t L, int32_t D, int32_t dtype, void* stream);
+
+/* Merge of the split rows of the forward: o = sum_i 2^(lse_i - M) o_i / sum_i 2^(lse_i - M), lse natural; with mask_rows the
+ * padded query rows get 0 and -inf. Grid of n_merge_cap CTAs. Replaces `split_merge_fwd` (csrc/vsa/split.cu:133-175). */
+int es_vsa_split_merge_fwd(const float* part_o, const float* part_lse, const int32_t* merges, const int32_t* info,
+                           int32_t n_merge_cap, const int32_t* blk_cnt, void* o, float* lse, int32_t L, int32_t D,
+                           int32_t mask_rows, int32_t dtype, void* stream);
+
+/* es_vsa_attn_bwd_kv / es_vsa_attn_bwd_q over a task list: chunk tasks write fp32 partial gradients part [slots, 64, D]
+ * without the per-block add. Replace `attn_bwd_tasks` and `attn_bwd_q_tasks` (csrc/vsa/vsa2_api.cpp:600-730). */
+int es_vsa_attn_bwd_kv_tasks(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                             const float* delta, void* dk, void* dv, float* dk_f32, float* dv_f32, const float* add_dk,
+                             const float* add_dv, int32_t add_nb, const int32_t* k2q_idx, const int32_t* blk_cnt,
+                             const int32_t* tasks, const int32_t* task_info, int32_t n_tasks_cap, float* part_dk,
+                             float* part_dv, int32_t BH, int32_t L, int32_t D, int32_t dtype, void* stream);
+int es_vsa_attn_bwd_q_tasks(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                            const float* delta, void* dq, float* dq_f32, const float* add_dq, int32_t add_nb,
+                            const int32_t* q2k_idx, const int32_t* blk_cnt, const int32_t* tasks, const int32_t* task_info,
+                            int32_t n_tasks_cap, float* part_dq, int32_t BH, int32_t L, int32_t D, int32_t dtype,
+                            void* stream);
+
+/* Merge of split rows of a backward pass, in chunk order: out = valid ? sum_i part_i + add[block] / count : 0, in the element
+ * type (out) or fp32 (out_f32). Replaces `split_merge_sum` (csrc/vsa/split.cu:177-228). */
+int es_vsa_split_merge_sum(const float* part, const int32_t* merges, const int32_t* info, int32_t n_merge_cap,
+                           const float* add, int32_t add_nb, const int32_t* blk_cnt, void* out, float* out_f32, int32_t L,
+                           int32_t D, int32_t dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

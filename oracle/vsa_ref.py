@@ -188,3 +188,41 @@ def tier_fine_attention(q, k, v, blk_cnt, tier_a, tier_ab, mid_reps=4, round_rep
                 lse = torch.logsumexp(s, -1)
                 lse_all[b, h, i * BLOCK:(i + 1) * BLOCK] = torch.where(row_ok, lse, torch.full_like(lse, float("-inf")))
     return o_all, lse_all
+
+
+# ------------------------------------------------------------------------------------------- split-KV plan
+def split_plan(ptr, chunk, max_slots, min_len=0, rel_mean=0.0, tail_frac=0.0, resident=1, budget=-1):
+    """Task plan of a CSR list ptr [B,H,NB+1] (reference: csrc/vsa/split.cu:1-22; its own Python statement of the same
+    contract is tests/test_vsa2_split.py:60-87). Returns (tasks [T,4], merges [M,4], info [8]) as int lists.
+
+    A row of n edges is eligible when n >= max(chunk + 1, min_len, ceil(tail_frac * W / resident),
+    ceil(rel_mean * edges of its (b, h) / NB)); eligible rows have ceil(n / chunk) chunks; nothing splits when more
+    than `budget` rows are eligible; a row splits while the running chunk count of the eligible rows (whether they
+    split or not) stays <= max_slots. Split chunks first (slot = task index), then one direct task per other row."""
+    import numpy as np
+    p = ptr.reshape(-1, ptr.shape[-1]).cpu().numpy().astype(np.int64)
+    BH, nb = p.shape[0], p.shape[1] - 1
+    W = int(p[-1, -1] - p[0, 0])
+    gthr = max(chunk + 1, min_len)
+    if tail_frac > 0:
+        gthr = max(gthr, math.ceil(tail_frac * W / resident))
+    budget = 2 ** 31 - 1 if budget < 0 else budget
+    n = (p[:, 1:] - p[:, :-1]).reshape(-1)
+    beg = p[:, :-1].reshape(-1)
+    thr = np.full(BH, gthr, dtype=np.int64)
+    if rel_mean > 0:
+        thr = np.maximum(thr, np.ceil(rel_mean * (p[:, nb] - p[:, 0]) / nb).astype(np.int64))
+    elig = n >= np.repeat(thr, nb)
+    c = np.where(elig, -(-n // chunk), 0)
+    E = int(elig.sum())
+    split = (E <= budget) & (c > 0) & (np.cumsum(c) <= max_slots)
+    tasks, merges = [], []
+    slot = 0
+    for r in np.nonzero(split)[0]:
+        cr, nr, br = int(c[r]), int(n[r]), int(beg[r])
+        merges.append([int(r), slot, cr, 0])
+        tasks += [[int(r), br + j * nr // cr, br + (j + 1) * nr // cr, slot + j] for j in range(cr)]
+        slot += cr
+    t_split = slot
+    tasks += [[int(r), int(beg[r]), int(beg[r] + n[r]), -1] for r in np.nonzero(~split)[0]]
+    return tasks, merges, [len(tasks), len(merges), t_split, BH * nb, E, int(E <= budget), gthr, W]

@@ -48,11 +48,19 @@ SIGNATURES = {
     "es_vsa_fuse_fwd": [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "es_vsa_fuse_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "es_vsa_finalize": [_P, _P, _P, _P, _I, _I, _I, _I, _I, _P],
+    "es_vsa_split_plan_workspace_bytes": [_I, _I],
+    "es_vsa_split_plan": [_P, _I, _I, _I, _I, _I, ctypes.c_double, ctypes.c_double, _I, _I, _P, _P, _P, _P, _P],
+    "es_vsa_attn_fwd_tasks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _P],
+    "es_vsa_split_merge_fwd": [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _P],
+    "es_vsa_attn_bwd_kv_tasks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _I, _I,
+                                 _I, _I, _P],
+    "es_vsa_attn_bwd_q_tasks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
+    "es_vsa_split_merge_sum": [_P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P],
     "es_debug_set_trace": [_P],
     "es_debug_trace_words": [],
 }
 _RESTYPES = {"es_last_error": ctypes.c_char_p, "es_launch_count": ctypes.c_longlong,
-             "es_vsa_topk_workspace_bytes": ctypes.c_longlong}
+             "es_vsa_topk_workspace_bytes": ctypes.c_longlong, "es_vsa_split_plan_workspace_bytes": ctypes.c_longlong}
 
 _lib = None
 

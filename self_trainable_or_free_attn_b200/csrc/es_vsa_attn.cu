@@ -25,19 +25,41 @@ struct FwdArgs {
     const int *row_ptr, *col_idx, *blk_cnt;
     int L, NB;
     float scale_log2;
+    // Split-KV task mode (es_vsa_split_plan), all null in the plain (block, bh) grid: tasks[t] = {row = bh * NB + block,
+    // first edge, one past the last edge, slot}; slot < 0 writes o / lse, slot >= 0 writes the fp32 normalised partial
+    // part_o[slot] [64, D] and its log2-domain lse part_lse[slot] [64].
+    const int* tasks;
+    const int* task_info;
+    float* part_o;
+    float* part_lse;
 };
+
+// The work item of a CTA: (block, bh) of the grid, or a task of the split plan. False: nothing to do.
+__device__ __forceinline__ bool work_item(const int* tasks, const int* info, const int* row_ptr, int NB, int& blk, int& bh,
+                                          int& beg, int& end, int& slot) {
+    if (tasks) {
+        if ((int)blockIdx.x >= info[0]) return false;
+        const int4 t = reinterpret_cast<const int4*>(tasks)[blockIdx.x];
+        bh = t.x / NB; blk = t.x - bh * NB; beg = t.y; end = t.z; slot = t.w;
+    } else {
+        blk = blockIdx.x; bh = blockIdx.y; slot = -1;
+        beg = row_ptr[(size_t)bh * (NB + 1) + blk];
+        end = row_ptr[(size_t)bh * (NB + 1) + blk + 1];
+    }
+    return true;
+}
 
 template <typename T, int D>
 __global__ void __launch_bounds__(128) attn_fwd_kernel(const FwdArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t TILE = TB * D * 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qb = blockIdx.x, bh = blockIdx.y;
+    int qb, bh, beg, end, slot;
+    if (!work_item(a.tasks, a.task_info, a.row_ptr, a.NB, qb, bh, beg, end, slot)) return;
     const uint32_t sQ = smem_addr(smem), sKV = sQ + TILE;           // [stage][K, V]
     const T* q = static_cast<const T*>(a.q) + ((size_t)bh * a.L + (size_t)qb * TB) * D;
     const T* kbase = static_cast<const T*>(a.k) + (size_t)bh * a.L * D;
     const T* vbase = static_cast<const T*>(a.v) + (size_t)bh * a.L * D;
-    const int beg = a.row_ptr[(size_t)bh * (a.NB + 1) + qb], end = a.row_ptr[(size_t)bh * (a.NB + 1) + qb + 1];
     const int n = end - beg;
     const int cnt_q = a.blk_cnt[qb];
 
@@ -131,6 +153,22 @@ __global__ void __launch_bounds__(128) attn_fwd_kernel(const FwdArgs a) {
 
     l0 = quad_sum(l0); l1 = quad_sum(l1);
     const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+    if (slot >= 0) {
+        // a chunk of a split row: the normalised partial and its log2 lse; the merge masks the padded rows
+        const float i0 = l0 > 0.f ? 1.f / l0 : 0.f, i1 = l1 > 0.f ? 1.f / l1 : 0.f;
+        float* po = a.part_o + (size_t)slot * TB * D;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            const int c = i * 8 + 2 * (lane & 3);
+            *reinterpret_cast<float2*>(po + (size_t)r0 * D + c) = make_float2(o[i][0] * i0, o[i][1] * i0);
+            *reinterpret_cast<float2*>(po + (size_t)r1 * D + c) = make_float2(o[i][2] * i1, o[i][3] * i1);
+        }
+        if ((lane & 3) == 0) {
+            a.part_lse[(size_t)slot * TB + r0] = l0 > 0.f ? m0 + log2f(l0) : -INFINITY;
+            a.part_lse[(size_t)slot * TB + r1] = l1 > 0.f ? m1 + log2f(l1) : -INFINITY;
+        }
+        return;
+    }
     const bool ok0 = r0 < cnt_q && l0 > 0.f, ok1 = r1 < cnt_q && l1 > 0.f;
     const float i0 = ok0 ? 1.f / l0 : 0.f, i1 = ok1 ? 1.f / l1 : 0.f;
     T* out = static_cast<T*>(a.o) + ((size_t)bh * a.L + (size_t)qb * TB) * D;
@@ -158,6 +196,11 @@ struct BwdArgs {
     const int *row_ptr, *col_idx, *blk_cnt;
     int L, NB;
     float scale, scale_log2;
+    // Split-KV task mode over the walked lists (see FwdArgs): slot >= 0 writes fp32 partial gradients to part0 / part1
+    // [slot] [64, D] without the per-block add (the merge adds it once and zeroes the padded rows).
+    const int* tasks;
+    const int* task_info;
+    float *part0, *part1;
 };
 
 template <typename T, int D>
@@ -184,6 +227,17 @@ __device__ __forceinline__ void store_rows(const BwdArgs& a, float (&acc)[D / 8]
     }
 }
 
+template <int D>
+__device__ __forceinline__ void store_part(float (&acc)[D / 8][4], float* dst, int warp, int lane, float mul) {
+    const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) {
+        const int c = i * 8 + 2 * (lane & 3);
+        *reinterpret_cast<float2*>(dst + (size_t)r0 * D + c) = make_float2(acc[i][0] * mul, acc[i][1] * mul);
+        *reinterpret_cast<float2*>(dst + (size_t)r1 * D + c) = make_float2(acc[i][2] * mul, acc[i][3] * mul);
+    }
+}
+
 // One CTA per kv block j: walks the query blocks i that selected it. Per pair, with S^T = K Q^T (kv rows x q columns):
 //   P^T = exp(scale S^T - lse_q), dV += P^T dO, dP^T = V dO^T, dS^T = P^T (dP^T - delta_q), dK += scale dS^T Q.
 template <typename T, int D>
@@ -191,13 +245,13 @@ __global__ void __launch_bounds__(128) attn_bwd_kv_kernel(const BwdArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t TILE = TB * D * 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int kb = blockIdx.x, bh = blockIdx.y;
+    int kb, bh, beg, end, slot;
+    if (!work_item(a.tasks, a.task_info, a.row_ptr, a.NB, kb, bh, beg, end, slot)) return;
     const uint32_t sK = smem_addr(smem), sV = sK + TILE, sQD = sV + TILE;      // [stage][Q, dO]
     float* sLse = reinterpret_cast<float*>(smem + 6 * TILE);                   // [stage][lse 64, delta 64]
     const size_t seq = (size_t)bh * a.L;
     const T* qbase = static_cast<const T*>(a.q) + seq * D;
     const T* dobase = static_cast<const T*>(a.dout) + seq * D;
-    const int beg = a.row_ptr[(size_t)bh * (a.NB + 1) + kb], end = a.row_ptr[(size_t)bh * (a.NB + 1) + kb + 1];
     const int n = end - beg;
     const int cnt_k = a.blk_cnt[kb];
 
@@ -290,6 +344,11 @@ __global__ void __launch_bounds__(128) attn_bwd_kv_kernel(const BwdArgs a) {
         __syncthreads();
     }
     cp_wait<0>();
+    if (slot >= 0) {
+        store_part<D>(dk, a.part0 + (size_t)slot * TB * D, warp, lane, a.scale);
+        store_part<D>(dv, a.part1 + (size_t)slot * TB * D, warp, lane, 1.f);
+        return;
+    }
     store_rows<T, D>(a, dk, a.d0, a.f0, a.add0, bh, kb, cnt_k, warp, lane, a.scale);
     store_rows<T, D>(a, dv, a.d1, a.f1, a.add1, bh, kb, cnt_k, warp, lane, 1.f);
 }
@@ -301,12 +360,12 @@ __global__ void __launch_bounds__(128) attn_bwd_q_kernel(const BwdArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     constexpr uint32_t TILE = TB * D * 2;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int qb = blockIdx.x, bh = blockIdx.y;
+    int qb, bh, beg, end, slot;
+    if (!work_item(a.tasks, a.task_info, a.row_ptr, a.NB, qb, bh, beg, end, slot)) return;
     const uint32_t sQ = smem_addr(smem), sDO = sQ + TILE, sKV = sDO + TILE;
     const size_t seq = (size_t)bh * a.L;
     const T* kbase = static_cast<const T*>(a.k) + seq * D;
     const T* vbase = static_cast<const T*>(a.v) + seq * D;
-    const int beg = a.row_ptr[(size_t)bh * (a.NB + 1) + qb], end = a.row_ptr[(size_t)bh * (a.NB + 1) + qb + 1];
     const int n = end - beg;
     const int cnt_q = a.blk_cnt[qb];
 
@@ -385,6 +444,10 @@ __global__ void __launch_bounds__(128) attn_bwd_q_kernel(const BwdArgs a) {
         __syncthreads();
     }
     cp_wait<0>();
+    if (slot >= 0) {
+        store_part<D>(dq, a.part0 + (size_t)slot * TB * D, warp, lane, a.scale);
+        return;
+    }
     store_rows<T, D>(a, dq, a.d0, a.f0, a.add0, bh, qb, cnt_q, warp, lane, a.scale);
 }
 
@@ -476,6 +539,77 @@ extern "C" int es_vsa_attn_bwd_q(const void* q, const void* k, const void* v, co
     cudaStream_t st = (cudaStream_t)stream;
     const size_t smem = (size_t)6 * TB * D * 2;
     const dim3 grid(L / TB, BH);
+    VSA_DISPATCH(attn_bwd_q_kernel, smem, grid, a);
+    ES_CHECK_LAUNCH("attn_bwd_q_kernel");
+    return 0;
+}
+
+// ---------------------------------------------------------------------------------------------- split-KV task launches
+static int check_tasks(const char* name, const int32_t* tasks, const int32_t* info, int n_tasks_cap) {
+    if (!tasks || !info) return set_error(-1, (std::string(name) + ": null task list").c_str());
+    if (n_tasks_cap <= 0) return set_error(-1, (std::string(name) + ": the task grid is empty").c_str());
+    if ((uintptr_t)tasks & 15) return set_error(-1, (std::string(name) + ": tasks must be 16-byte aligned").c_str());
+    return 0;
+}
+
+extern "C" int es_vsa_attn_fwd_tasks(const void* q, const void* k, const void* v, void* o, float* lse,
+                                     const int32_t* q2k_idx, const int32_t* blk_cnt, const int32_t* tasks,
+                                     const int32_t* task_info, int32_t n_tasks_cap, float* part_o, float* part_lse,
+                                     int32_t BH, int32_t L, int32_t D, int32_t dtype, void* stream) {
+    if (!q || !k || !v || !o || !lse || !q2k_idx || !blk_cnt) return set_error(-1, "es_vsa_attn_fwd_tasks: null pointer");
+    if (int rc = check_common("es_vsa_attn_fwd_tasks", BH, L, D, dtype)) return rc;
+    if (int rc = check_tasks("es_vsa_attn_fwd_tasks", tasks, task_info, n_tasks_cap)) return rc;
+    FwdArgs a{q, k, v, o, lse, nullptr, q2k_idx, blk_cnt, L, L / TB, LOG2E / sqrtf((float)D), tasks, task_info, part_o, part_lse};
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t smem = (size_t)5 * TB * D * 2;
+    const dim3 grid(n_tasks_cap, 1);
+    VSA_DISPATCH(attn_fwd_kernel, smem, grid, a);
+    ES_CHECK_LAUNCH("attn_fwd_kernel");
+    return 0;
+}
+
+extern "C" int es_vsa_attn_bwd_kv_tasks(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                                        const float* delta, void* dk, void* dv, float* dk_f32, float* dv_f32,
+                                        const float* add_dk, const float* add_dv, int32_t add_nb, const int32_t* k2q_idx,
+                                        const int32_t* blk_cnt, const int32_t* tasks, const int32_t* task_info,
+                                        int32_t n_tasks_cap, float* part_dk, float* part_dv, int32_t BH, int32_t L,
+                                        int32_t D, int32_t dtype, void* stream) {
+    if (!q || !k || !v || !dout || !lse || !delta || !k2q_idx || !blk_cnt)
+        return set_error(-1, "es_vsa_attn_bwd_kv_tasks: null pointer");
+    if ((!dk && !dk_f32) || (!dv && !dv_f32)) return set_error(-1, "es_vsa_attn_bwd_kv_tasks: no output for dK or dV");
+    if ((add_dk || add_dv) && add_nb < L / TB) return set_error(-1, "es_vsa_attn_bwd_kv_tasks: add_nb smaller than the block count");
+    if (int rc = check_common("es_vsa_attn_bwd_kv_tasks", BH, L, D, dtype)) return rc;
+    if (int rc = check_tasks("es_vsa_attn_bwd_kv_tasks", tasks, task_info, n_tasks_cap)) return rc;
+    BwdArgs a{};
+    fill_bwd(a, q, k, v, dout, lse, delta, nullptr, k2q_idx, blk_cnt, L, D);
+    a.d0 = dk; a.d1 = dv; a.f0 = dk_f32; a.f1 = dv_f32; a.add0 = add_dk; a.add1 = add_dv; a.add_nb = add_nb;
+    a.tasks = tasks; a.task_info = task_info; a.part0 = part_dk; a.part1 = part_dv;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t smem = (size_t)6 * TB * D * 2 + 2 * 128 * sizeof(float);
+    const dim3 grid(n_tasks_cap, 1);
+    VSA_DISPATCH(attn_bwd_kv_kernel, smem, grid, a);
+    ES_CHECK_LAUNCH("attn_bwd_kv_kernel");
+    return 0;
+}
+
+extern "C" int es_vsa_attn_bwd_q_tasks(const void* q, const void* k, const void* v, const void* dout, const float* lse,
+                                       const float* delta, void* dq, float* dq_f32, const float* add_dq, int32_t add_nb,
+                                       const int32_t* q2k_idx, const int32_t* blk_cnt, const int32_t* tasks,
+                                       const int32_t* task_info, int32_t n_tasks_cap, float* part_dq, int32_t BH,
+                                       int32_t L, int32_t D, int32_t dtype, void* stream) {
+    if (!q || !k || !v || !dout || !lse || !delta || !q2k_idx || !blk_cnt)
+        return set_error(-1, "es_vsa_attn_bwd_q_tasks: null pointer");
+    if (!dq && !dq_f32) return set_error(-1, "es_vsa_attn_bwd_q_tasks: no output for dQ");
+    if (add_dq && add_nb < L / TB) return set_error(-1, "es_vsa_attn_bwd_q_tasks: add_nb smaller than the block count");
+    if (int rc = check_common("es_vsa_attn_bwd_q_tasks", BH, L, D, dtype)) return rc;
+    if (int rc = check_tasks("es_vsa_attn_bwd_q_tasks", tasks, task_info, n_tasks_cap)) return rc;
+    BwdArgs a{};
+    fill_bwd(a, q, k, v, dout, lse, delta, nullptr, q2k_idx, blk_cnt, L, D);
+    a.d0 = dq; a.f0 = dq_f32; a.add0 = add_dq; a.add_nb = add_nb;
+    a.tasks = tasks; a.task_info = task_info; a.part0 = part_dq;
+    cudaStream_t st = (cudaStream_t)stream;
+    const size_t smem = (size_t)6 * TB * D * 2;
+    const dim3 grid(n_tasks_cap, 1);
     VSA_DISPATCH(attn_bwd_q_kernel, smem, grid, a);
     ES_CHECK_LAUNCH("attn_bwd_q_kernel");
     return 0;

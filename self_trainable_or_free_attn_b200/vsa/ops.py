@@ -193,6 +193,206 @@ def _bwd_q(q, k, v, dout, lse, delta, ptr, idx, cnt, add_dq=None, f32=False):
     return dq
 
 
+# ------------------------------------------------------------------------------------------- split-KV scheduling
+@dataclass(frozen=True)
+class SplitPolicy:
+    """Automatic per-direction choice of the lists worth splitting (reference: echosparse/vsa/ops.py:226-262).
+
+    A list of n blocks is eligible when n >= max(min_chunks * chunk, chunk + 1, rel_mean * (mean list length of its
+    head), tail_frac * (all edges of that direction) / resident CTAs); if more than waves * resident lists are eligible
+    nothing is split in that direction. resident = SMs x CTAs per SM of the consuming kernel, or `resident_ctas`."""
+    rel_mean: float = 4.0
+    tail_frac: float = 0.05
+    min_chunks: int = 2
+    fwd_waves: float = 1.0
+    bwd_waves: float = 8.0
+    max_task_waves: int = 64
+    resident_ctas: Optional[int] = None
+
+    def __post_init__(self):
+        for name in ("rel_mean", "tail_frac", "fwd_waves", "bwd_waves"):
+            v = getattr(self, name)
+            if isinstance(v, bool) or not isinstance(v, (int, float)):
+                raise TypeError(f"SplitPolicy.{name} must be a real number, got {type(v).__name__}")
+            if not math.isfinite(v) or v < 0:
+                raise ValueError(f"SplitPolicy.{name} must be finite and >= 0, got {v!r}")
+        for name in ("min_chunks", "max_task_waves", "resident_ctas"):
+            v = getattr(self, name)
+            if v is None and name == "resident_ctas":
+                continue
+            if isinstance(v, bool) or not isinstance(v, int):
+                raise TypeError(f"SplitPolicy.{name} must be an int, got {type(v).__name__}")
+            if v < 1:
+                raise ValueError(f"SplitPolicy.{name} must be >= 1, got {v!r}")
+
+
+@dataclass(frozen=True)
+class SplitKV:
+    """Balanced split-KV scheduling of the fine attention (reference: echosparse/vsa/ops.py:265-305). A query block
+    (forward, dQ pass) or kv block (dK / dV pass) whose list is chosen runs as ceil(n / chunk) balanced chunk tasks; the
+    chunks write fp32 partials that are merged per block in chunk order (deterministic). Without `policy` every list
+    longer than `chunk` is chosen; with a SplitPolicy (`SplitKV.auto()`) the planner on the GPU picks the clearly long
+    ones per direction. Partials are capped at `max_scratch_bytes` per stage (later long lists run unsplit)."""
+    chunk: int = 64
+    fwd: bool = True
+    bwd: bool = True
+    max_scratch_bytes: int = 1 << 30
+    policy: Optional[SplitPolicy] = None
+
+    def __post_init__(self):
+        if not 1 <= int(self.chunk) <= 1 << 30:
+            raise ValueError(f"SplitKV.chunk must be in [1, 2**30], got {self.chunk}")
+        if int(self.max_scratch_bytes) < 0:
+            raise ValueError("SplitKV.max_scratch_bytes must be >= 0")
+        if self.policy is not None and not isinstance(self.policy, SplitPolicy):
+            raise TypeError("SplitKV.policy must be a SplitPolicy or None")
+
+    @classmethod
+    def auto(cls, chunk=64, fwd=True, bwd=True, max_scratch_bytes=64 << 20, policy=None):
+        return cls(chunk=chunk, fwd=fwd, bwd=bwd, max_scratch_bytes=max_scratch_bytes, policy=policy or SplitPolicy())
+
+
+def split_slots(nnz, chunk, slot_bytes, max_bytes):
+    """Partial slots of a plan: max_bytes // slot_bytes, and never more than a split plan can use (2 * ceil(nnz / chunk))."""
+    return max(0, min(int(max_bytes) // int(slot_bytes), 2 * (-(-int(nnz) // int(chunk)))))
+
+
+# resident CTAs per SM of the kernels that consume a plan (shared memory: 80 KB forward, 97 KB dK / dV, 96 KB dQ at D = 128)
+_CTAS_PER_SM = {("fwd", 64): 5, ("fwd", 128): 2, ("bwd_kv", 64): 4, ("bwd_kv", 128): 2, ("bwd_q", 64): 4, ("bwd_q", 128): 2}
+
+
+def split_resident(q, kind, policy=None):
+    if policy is not None and policy.resident_ctas is not None:
+        return int(policy.resident_ctas)
+    return torch.cuda.get_device_properties(q.device).multi_processor_count * _CTAS_PER_SM[(kind, q.shape[-1])]
+
+
+def split_plan(ptr, chunk, max_slots, min_len=0, rel_mean=0.0, tail_frac=0.0, resident=1, budget=-1):
+    """(tasks [NR + max_slots, 4], merges [max(1, min(NR, max_slots // 2)), 4], info [8]) int32 on the device."""
+    B, H, n1 = ptr.shape
+    nr = B * H * (n1 - 1)
+    i32 = dict(device=ptr.device, dtype=torch.int32)
+    tasks = torch.empty(nr + max_slots, 4, **i32)
+    merges = torch.empty(max(1, min(nr, max_slots // 2)), 4, **i32)
+    info = torch.empty(8, **i32)
+    lib = N.load()
+    ws = torch.empty(int(lib.es_vsa_split_plan_workspace_bytes(B * H, n1 - 1)), device=ptr.device, dtype=torch.uint8)
+    N.check(lib.es_vsa_split_plan(N.ptr(ptr), B * H, n1 - 1, int(chunk), int(max_slots), max(int(chunk) + 1, int(min_len)),
+                                  float(rel_mean), float(tail_frac), int(resident),
+                                  2 ** 31 - 1 if budget < 0 else int(budget), N.ptr(tasks), N.ptr(merges), N.ptr(info),
+                                  N.ptr(ws), N.stream_ptr()), "es_vsa_split_plan")
+    return tasks, merges, info
+
+
+def split_plan_for(q, ptr, idx, split, kind, slot_bytes):
+    """(tasks, merges, info, slots) of one direction. kind: fwd (q2k), bwd_kv (k2q), bwd_q (q2k)."""
+    nnz, nb = idx.numel(), ptr.shape[-1] - 1
+    slots = split_slots(nnz, split.chunk, slot_bytes, split.max_scratch_bytes)
+    pol = split.policy
+    if pol is None:
+        return (*split_plan(ptr, split.chunk, slots), slots)
+    resident = split_resident(q, kind, pol)
+    budget = int((pol.fwd_waves if kind == "fwd" else pol.bwd_waves) * resident)
+    slots = min(slots, budget * (-(-nb // split.chunk)), pol.max_task_waves * resident)
+    plan = split_plan(ptr, split.chunk, slots, max(split.chunk + 1, pol.min_chunks * split.chunk), pol.rel_mean,
+                      pol.tail_frac, resident, budget)
+    return (*plan, slots)
+
+
+def split_fine_fwd(q, k, v, ptr, idx, blk_cnt, split):
+    """Balanced fine forward: plan, chunk / direct tasks, merge. Returns (O_f, lse) like attn_fwd."""
+    B, H, L, D = q.shape
+    tasks, merges, info, slots = split_plan_for(q, ptr, idx, split, "fwd", 64 * (D + 1) * 4)
+    part_o = torch.empty(max(slots, 1), 64, D, device=q.device, dtype=torch.float32)
+    part_lse = torch.empty(max(slots, 1), 64, device=q.device, dtype=torch.float32)
+    o = torch.empty_like(q)
+    lse = torch.empty(B, H, L, device=q.device, dtype=torch.float32)
+    lib, dt, st = N.load(), _DTYPES[q.dtype], N.stream_ptr()
+    N.check(lib.es_vsa_attn_fwd_tasks(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(o), N.ptr(lse), N.ptr(idx), N.ptr(blk_cnt),
+                                      N.ptr(tasks), N.ptr(info), tasks.shape[0], N.ptr(part_o), N.ptr(part_lse), B * H, L,
+                                      D, dt, st), "es_vsa_attn_fwd_tasks")
+    if slots:
+        N.check(lib.es_vsa_split_merge_fwd(N.ptr(part_o), N.ptr(part_lse), N.ptr(merges), N.ptr(info), merges.shape[0],
+                                           N.ptr(blk_cnt), N.ptr(o), N.ptr(lse), L, D, 1, dt, st), "es_vsa_split_merge_fwd")
+    return o, lse
+
+
+def _merge_sum(part, merges, info, add, blk_cnt, out, L, D, dt):
+    N.check(N.load().es_vsa_split_merge_sum(N.ptr(part), N.ptr(merges), N.ptr(info), merges.shape[0], N.ptr(add),
+                                            add.shape[2] if add is not None else 0, N.ptr(blk_cnt), N.ptr(out), None, L, D,
+                                            dt, N.stream_ptr()), "es_vsa_split_merge_sum")
+
+
+def split_fine_bwd(q, k, v, dout, lse, delta, sel, blk_cnt, dqc, dkc, dvc, split):
+    """Balanced fine backward: the dK / dV pass over a plan of the kv -> q lists, the dQ pass over one of the q -> kv lists."""
+    B, H, L, D = q.shape
+    lib, dt, st = N.load(), _DTYPES[q.dtype], N.stream_ptr()
+    f32 = dict(device=q.device, dtype=torch.float32)
+    add_nb = dkc.shape[2] if dkc is not None else 0
+    tasks, merges, info, slots = split_plan_for(q, sel.k2q_ptr, sel.k2q_idx, split, "bwd_kv", 2 * 64 * D * 4)
+    part_dk, part_dv = torch.empty(max(slots, 1), 64, D, **f32), torch.empty(max(slots, 1), 64, D, **f32)
+    dk, dv = torch.empty_like(q), torch.empty_like(q)
+    N.check(lib.es_vsa_attn_bwd_kv_tasks(
+        N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(dout), N.ptr(lse), N.ptr(delta), N.ptr(dk), N.ptr(dv), None, None, N.ptr(dkc),
+        N.ptr(dvc), add_nb, N.ptr(sel.k2q_idx), N.ptr(blk_cnt), N.ptr(tasks), N.ptr(info), tasks.shape[0], N.ptr(part_dk),
+        N.ptr(part_dv), B * H, L, D, dt, st), "es_vsa_attn_bwd_kv_tasks")
+    if slots:
+        _merge_sum(part_dk, merges, info, dkc, blk_cnt, dk, L, D, dt)
+        _merge_sum(part_dv, merges, info, dvc, blk_cnt, dv, L, D, dt)
+    del part_dk, part_dv
+    tasks, merges, info, slots = split_plan_for(q, sel.q2k_ptr, sel.q2k_idx, split, "bwd_q", 64 * D * 4)
+    part_dq = torch.empty(max(slots, 1), 64, D, **f32)
+    dq = torch.empty_like(q)
+    N.check(lib.es_vsa_attn_bwd_q_tasks(
+        N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(dout), N.ptr(lse), N.ptr(delta), N.ptr(dq), None, N.ptr(dqc), add_nb,
+        N.ptr(sel.q2k_idx), N.ptr(blk_cnt), N.ptr(tasks), N.ptr(info), tasks.shape[0], N.ptr(part_dq), B * H, L, D, dt, st),
+        "es_vsa_attn_bwd_q_tasks")
+    if slots:
+        _merge_sum(part_dq, merges, info, dqc, blk_cnt, dq, L, D, dt)
+    return dq, dk, dv
+
+
+def _check_split(split):
+    if split is None:
+        return None
+    if isinstance(split, str) and split == "auto":
+        return SplitKV.auto()
+    if not isinstance(split, SplitKV):
+        raise TypeError(f"split_kv must be a SplitKV, 'auto' or None, got {type(split).__name__}")
+    return split
+
+
+def describe_split(q, selection, split):
+    """Diagnostic (synchronises): the plans the operator would build for this selection, per direction."""
+    out = {}
+    D = q.shape[-1]
+    dirs = []
+    if split.fwd:
+        dirs.append(("fwd", selection.q2k_ptr, selection.q2k_idx, 64 * (D + 1) * 4))
+    if split.bwd:
+        dirs.append(("bwd_kv", selection.k2q_ptr, selection.k2q_idx, 2 * 64 * D * 4))
+        dirs.append(("bwd_q", selection.q2k_ptr, selection.q2k_idx, 64 * D * 4))
+    names = ["tasks", "split_rows", "split_slots", "rows", "eligible_rows", "within_budget", "global_threshold", "edges"]
+    for kind, ptr, idx, sb in dirs:
+        _, merges, info, slots = split_plan_for(q, ptr, idx, split, kind, sb)
+        out[kind] = dict(info=dict(zip(names, info.tolist())), max_slots=slots,
+                         resident=split_resident(q, kind, split.policy) if split.policy else None)
+    return out
+
+
+def _fine_fwd(q, k, v, sel, blk_cnt, split):
+    if split is not None and split.fwd:
+        return split_fine_fwd(q, k, v, sel.q2k_ptr, sel.q2k_idx, blk_cnt, split)
+    return attn_fwd(q, k, v, sel.q2k_ptr, sel.q2k_idx, blk_cnt)
+
+
+def _fine_bwd(q, k, v, dout, lse, delta, sel, blk_cnt, dqc, dkc, dvc, split):
+    if split is not None and split.bwd:
+        return split_fine_bwd(q, k, v, dout, lse, delta, sel, blk_cnt, dqc, dkc, dvc, split)
+    dk, dv = _bwd_kv(q, k, v, dout, lse, delta, sel.k2q_ptr, sel.k2q_idx, blk_cnt, add_dk=dkc, add_dv=dvc)
+    return _bwd_q(q, k, v, dout, lse, delta, sel.q2k_ptr, sel.q2k_idx, blk_cnt, add_dq=dqc), dk, dv
+
+
 def _gate_mode(gate, q):
     if gate is None:
         return 0
@@ -219,14 +419,14 @@ def _fuse_bwd(dout, of, oc, gate, blk_cnt, gate_act):
 
 class _Function(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, gate, blk_cnt, R, budget, row_norm, gate_act, sel_in):
+    def forward(ctx, q, k, v, gate, blk_cnt, R, budget, row_norm, gate_act, sel_in, split):
         B, H, L, D = q.shape
         nb = L // 64
         qr, kr, qc, kc, vc = pool_fwd(q, k, v, blk_cnt, R)
         c_cnt, c_ptr, c_idx = _coarse_meta(B, H, nb, qc.shape[2], q.device)
         oc, lse_c = attn_fwd(qc, kc, vc, c_ptr, c_idx, c_cnt)
         sel = sel_in if sel_in is not None else _route(qr, kr, blk_cnt, R, budget, row_norm)
-        of, lse_f = attn_fwd(q, k, v, sel.q2k_ptr, sel.q2k_idx, blk_cnt)
+        of, lse_f = _fine_fwd(q, k, v, sel, blk_cnt, split)
         o = torch.empty_like(q)
         N.check(N.load().es_vsa_fuse_fwd(N.ptr(of), N.ptr(oc), N.ptr(gate), N.ptr(o), N.ptr(blk_cnt), B * H, L, D,
                                          oc.shape[2], _gate_mode(gate, q), gate_act, _DTYPES[q.dtype], N.stream_ptr()),
@@ -236,6 +436,7 @@ class _Function(torch.autograd.Function):
         ctx.inter = [qc, kc, vc, oc, lse_c, of, lse_f, sel, c_cnt, c_ptr, c_idx]
         ctx.has_gate = gate is not None
         ctx.gate_act = gate_act
+        ctx.split = split
         ctx.mark_non_differentiable(sel.q2k_ptr, sel.q2k_idx, sel.k2q_ptr, sel.k2q_idx)
         return o, sel.q2k_ptr, sel.q2k_idx, sel.k2q_ptr, sel.k2q_idx
 
@@ -254,19 +455,19 @@ class _Function(torch.autograd.Function):
         dkc, dvc = _bwd_kv(qc, kc, vc, dout_c, lse_c, delta_c, c_ptr, c_idx, c_cnt, f32=True)
         dqc = _bwd_q(qc, kc, vc, dout_c, lse_c, delta_c, c_ptr, c_idx, c_cnt, f32=True)
         # fine branch on the forward's selection, plus the unpooled coarse gradients (block gradient / count per token)
-        dk, dv = _bwd_kv(q, k, v, dout, lse_f, delta_f, sel.k2q_ptr, sel.k2q_idx, blk_cnt, add_dk=dkc, add_dv=dvc)
-        dq = _bwd_q(q, k, v, dout, lse_f, delta_f, sel.q2k_ptr, sel.q2k_idx, blk_cnt, add_dq=dqc)
+        dq, dk, dv = _fine_bwd(q, k, v, dout, lse_f, delta_f, sel, blk_cnt, dqc, dkc, dvc, ctx.split)
         ctx.inter = None
-        return (dq, dk, dv, dgate if ctx.has_gate else None) + (None,) * 6
+        return (dq, dk, dv, dgate if ctx.has_gate else None) + (None,) * 7
 
 
 def vsa2_attention(q, k, v, gate, blk_cnt, *, R=16, topk=None, budget=None, row_norm="paper", gate_act="tanh",
-                   backend="auto", selection: Optional[Selection] = None, return_selection=False):
+                   backend="auto", selection: Optional[Selection] = None, return_selection=False, split_kv=None):
     """Full VSA2 attention: O = O_fine + act(gate) * repeat(O_coarse).
 
     The router (pool R -> softmax over all pooled keys -> pool to 64-token blocks) and the exact global top-k (budget =
     NB * topk connections per (b, h)) run on every call unless a frozen `selection` is passed (testing). `backend` is kept
-    for signature compatibility; there is a single sm_100a backend.
+    for signature compatibility; there is a single sm_100a backend. `split_kv`: a SplitKV (manual), SplitKV.auto() or
+    "auto" (planner on the GPU), None (default) unsplit.
     """
     if backend not in ("auto", "generic"):
         raise ValueError(f"unknown backend {backend!r}: this build has the one sm_100a backend ('auto' or 'generic')")
@@ -282,7 +483,7 @@ def vsa2_attention(q, k, v, gate, blk_cnt, *, R=16, topk=None, budget=None, row_
         _gate_mode(gate, q)
     b = budget_from_topk(nb, topk, budget) if selection is None else 0
     o, qp, qi, kp, ki = _Function.apply(q, k, v, gate, blk_cnt, int(R), b, ROW_NORMS[row_norm], GATE_ACTS[gate_act],
-                                        selection)
+                                        selection, _check_split(split_kv))
     if return_selection:
         return o, Selection(qp, qi, kp, ki)
     return o
@@ -290,8 +491,9 @@ def vsa2_attention(q, k, v, gate, blk_cnt, *, R=16, topk=None, budget=None, row_
 
 class _FineFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, blk_cnt, sel):
-        of, lse = attn_fwd(q, k, v, sel.q2k_ptr, sel.q2k_idx, blk_cnt)
+    def forward(ctx, q, k, v, blk_cnt, sel, split):
+        of, lse = _fine_fwd(q, k, v, sel, blk_cnt, split)
+        ctx.split = split
         ctx.save_for_backward(q, k, v, blk_cnt, of, lse, sel.q2k_ptr, sel.q2k_idx, sel.k2q_ptr, sel.k2q_idx)
         ctx.mark_non_differentiable(lse)
         return of, lse
@@ -303,13 +505,12 @@ class _FineFunction(torch.autograd.Function):
         dout = dout.contiguous()
         oc0 = torch.zeros(B, H, _pad64(L // 64), D, device=q.device, dtype=q.dtype)
         delta_f, _, _, _ = _fuse_bwd(dout, of, oc0, None, blk_cnt, 0)
-        dk, dv = _bwd_kv(q, k, v, dout, lse, delta_f, kp, ki, blk_cnt)
-        dq = _bwd_q(q, k, v, dout, lse, delta_f, qp, qi, blk_cnt)
-        return dq, dk, dv, None, None
+        dq, dk, dv = _fine_bwd(q, k, v, dout, lse, delta_f, Selection(qp, qi, kp, ki), blk_cnt, None, None, None, ctx.split)
+        return dq, dk, dv, None, None, None
 
 
-def fine_block_sparse_attention(q, k, v, blk_cnt, selection: Selection, backend="auto"):
+def fine_block_sparse_attention(q, k, v, blk_cnt, selection: Selection, backend="auto", split_kv=None):
     """Diagnostic fine-only primitive (no coarse branch, no router). Returns (O_f, lse); query blocks without an edge and
     padded rows give O_f = 0 and lse = -inf."""
     _check_tokens(q, k, v)
-    return _FineFunction.apply(q, k, v, blk_cnt.to(torch.int32).contiguous(), selection)
+    return _FineFunction.apply(q, k, v, blk_cnt.to(torch.int32).contiguous(), selection, _check_split(split_kv))

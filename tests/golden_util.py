@@ -87,3 +87,48 @@ def vsa_tiers(nb):
     a[:, :, 1] = False
     ab[:, :, 1] = False
     return a, ab
+
+
+# ---------------------------------------------------------------------------------------------- split-KV plan cases
+POLICY = dict(min_len=4, rel_mean=4.0, tail_frac=0.05, resident=4)
+SPLIT_CASES = {   # name: (mask kind, NB, heads, chunk, max_slots, policy arguments)
+    "random_c2": ("random", 13, 4, 2, 10 ** 6, {}),
+    "random_c3_cap10": ("random", 13, 4, 3, 10, {}),
+    "hotq_c1_cap3": ("hotq", 13, 4, 1, 3, {}),
+    "hotkv_c64": ("hotkv", 13, 4, 64, 10 ** 6, {}),
+    "hotqkv_c2_cap0": ("hotqkv", 13, 4, 2, 0, {}),
+    "full_c3": ("full", 13, 4, 3, 10 ** 6, {}),
+    "policy_hotq": ("hotq", 24, 3, 2, 10 ** 6, dict(budget=16, **POLICY)),
+    "policy_hotkv": ("hotkv", 24, 3, 2, 10 ** 6, dict(budget=16, **POLICY)),
+    "policy_over_budget": ("hotqkv", 32, 4, 2, 10 ** 6, dict(budget=3, **POLICY)),
+    "policy_cap40": ("hotqkv", 32, 4, 2, 40, dict(budget=64, **POLICY)),
+}
+
+
+def split_mask(kind, heads, nb, seed=5):
+    """Skewed block masks [1, heads, NB, NB]: hot query rows, hot kv columns, both, with empty and single-edge rows."""
+    rs = np.random.RandomState(seed + nb)
+    u = lambda *s: torch.from_numpy(rs.random_sample(s))
+    m = torch.zeros(1, heads, nb, nb, dtype=torch.bool)
+    if kind == "full":
+        m[:] = True
+    elif kind == "random":
+        m = u(1, heads, nb, nb) < 0.3
+        m[:, :, 0] = False
+        m[:, :, -1] = True
+    elif kind == "hotq":
+        m[:, :, 1] = True
+        m[:, :, nb - 2] = u(1, heads, nb) < 0.8
+        m[:, :, 3, 5] = True
+    elif kind == "hotkv":
+        m = u(1, heads, nb, nb) < 2.0 / nb
+        m[..., 0] = True
+        m[..., nb - 1] = True
+        m[:, :, 2] = False
+    elif kind == "hotqkv":
+        m[:, :, : nb // 4] = u(1, heads, nb // 4, nb) < 0.7
+        m[..., 1] = True
+        m[:, :, nb // 2] = False
+    else:
+        raise ValueError(kind)
+    return m
