@@ -48,6 +48,11 @@ long long es_vsa_topk_workspace_bytes(int32_t bh_count, int32_t NB);
 int es_vsa_global_topk(const float* scores, int32_t NB, int32_t bh0, int32_t bh_count, long long budget, int32_t* q2k_ptr,
                        int32_t* q2k_idx, int32_t* k2q_ptr, int32_t* k2q_idx, void* workspace, void* stream);
 
+/* Byte offset, inside the workspace of es_vsa_global_topk, of the selection bitmap it leaves behind: [bh_count, NB,
+ * ceil(NB / 32)] uint32, bit j of row i set when (i, j) is selected (the `bits_a` / `bits_ab` of the tier router,
+ * experiments/vsa2_representative/csrc/rep/rep_api.cpp:90-170 `route_tiers`, which runs the same top-k at two budgets). */
+long long es_vsa_topk_bits_offset(int32_t bh_count, int32_t NB);
+
 /* Attention of every 64-row query block over the valid tokens of its listed kv blocks (online softmax): o [BH, L, D],
  * lse [BH, L]. Also the coarse branch (block means as a sequence, 64-row tiles with their own counts, dense lists).
  * Replaces `attn_fwd` (launch_attn_fwd, csrc/vsa/vsa2_kernels.h:146). */
@@ -87,6 +92,42 @@ int es_vsa_fuse_bwd(const void* dout, const void* of, const void* oc, const void
  * be NULL). Replaces `finalize` (launch_finalize, csrc/vsa/vsa2_kernels.h:306). */
 int es_vsa_finalize(const float* acc, const float* add, void* out, const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D,
                     int32_t add_nb, int32_t dtype, void* stream);
+
+/* ---- 64 / RM / 1 representative tiers (one softmax over: tokens of the tier-A blocks of the CSR list; the RM group means of
+ * the blocks in bits_ab & ~bits_a, each + log2(tokens in the group); the block means of the blocks in ~bits_ab, + log2(count)).
+ * Tables: k_mid, v_mid [BH, mid_stride, D] (row = block * RM + group) and k_tail, v_tail [BH, tail_stride, D] in the element
+ * type, strides padded to multiples of 64 rows: the pooled means of es_vsa_pool with R = 64 / RM. bits [BH, NB, ceil(NB/32)].
+ * phases: mask of 1 (A), 2 (B), 4 (C). mid_reps RM in {2, 4, 8, 16}. ---- */
+
+/* Forward of the three-tier fine branch. Replaces `rep_attn_fwd` (experiments/vsa2_representative/csrc/rep/rep_api.cpp:200-290). */
+int es_vsa_tier_attn_fwd(const void* q, const void* k, const void* v, const void* k_mid, const void* v_mid, const void* k_tail,
+                         const void* v_tail, void* o, float* lse, const int32_t* q2k_ptr, const int32_t* q2k_idx,
+                         const int32_t* bits_a, const int32_t* bits_ab, const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D,
+                         int32_t mid_reps, int32_t mid_stride, int32_t tail_stride, int32_t phases, int32_t dtype, void* stream);
+
+/* dQ over all three tiers, one owner per query block; add_dq as in es_vsa_attn_bwd_q.
+ * Replaces the dQ part of `rep_attn_bwd_q` (rep_api.cpp:292-400). */
+int es_vsa_tier_attn_bwd_q(const void* q, const void* k, const void* v, const void* k_mid, const void* v_mid,
+                           const void* k_tail, const void* v_tail, const void* dout, const float* lse, const float* delta,
+                           void* dq, const float* add_dq, int32_t add_nb, const int32_t* q2k_ptr, const int32_t* q2k_idx,
+                           const int32_t* bits_a, const int32_t* bits_ab, const int32_t* blk_cnt, int32_t BH, int32_t L,
+                           int32_t D, int32_t mid_reps, int32_t mid_stride, int32_t tail_stride, int32_t phases, int32_t dtype,
+                           void* stream);
+
+/* Gradients of the representative tables, fp32, shaped like the tables (zero-filled by the caller): one owner per table row, no
+ * atomics. Replaces the table accumulation of `rep_attn_bwd_q` (dk_mid, dv_mid, dk_tail, dv_tail; rep_api.cpp:292-400).
+ * Tier-A token gradients come from es_vsa_attn_bwd_kv on the tier-A kv -> q lists (`tier_a_bwd_kv`, rep_api.cpp:402-450). */
+int es_vsa_tier_rep_bwd(const void* q, const void* k_mid, const void* v_mid, const void* k_tail, const void* v_tail,
+                        const void* dout, const float* lse, const float* delta, float* dk_mid, float* dv_mid, float* dk_tail,
+                        float* dv_tail, const int32_t* bits_a, const int32_t* bits_ab, const int32_t* blk_cnt, int32_t BH,
+                        int32_t L, int32_t D, int32_t mid_reps, int32_t mid_stride, int32_t tail_stride, int32_t phases,
+                        int32_t dtype, void* stream);
+
+/* Token gradient from its three sources: out = valid ? tok + mid[group] / tokens in the group + (tail[block] + add[block]) /
+ * tokens in the block : 0; every fp32 source may be NULL. Replaces `rep_unpool` (rep_api.cpp:452-505). */
+int es_vsa_tier_unpool(const float* tok, const float* mid, const float* tail, const float* add, int32_t add_nb, void* out,
+                       const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D, int32_t mid_reps, int32_t mid_stride,
+                       int32_t tail_stride, int32_t dtype, void* stream);
 
 /* ---- split-KV scheduling (balanced chunk tasks for long lists) ----
  * Plan of one CSR list ptr [BH * (NB + 1)] (q -> kv for the forward and the dQ pass, kv -> q for the dK / dV pass). A row of n

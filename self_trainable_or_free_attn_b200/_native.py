@@ -56,11 +56,18 @@ SIGNATURES = {
                                  _I, _I, _P],
     "es_vsa_attn_bwd_q_tasks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
     "es_vsa_split_merge_sum": [_P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P],
+    "es_vsa_topk_bits_offset": [_I, _I],
+    "es_vsa_tier_attn_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "es_vsa_tier_attn_bwd_q": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
+                               _I, _I, _I, _P],
+    "es_vsa_tier_rep_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
+    "es_vsa_tier_unpool": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
     "es_debug_set_trace": [_P],
     "es_debug_trace_words": [],
 }
 _RESTYPES = {"es_last_error": ctypes.c_char_p, "es_launch_count": ctypes.c_longlong,
-             "es_vsa_topk_workspace_bytes": ctypes.c_longlong, "es_vsa_split_plan_workspace_bytes": ctypes.c_longlong}
+             "es_vsa_topk_workspace_bytes": ctypes.c_longlong, "es_vsa_split_plan_workspace_bytes": ctypes.c_longlong,
+             "es_vsa_topk_bits_offset": ctypes.c_longlong}
 
 _lib = None
 

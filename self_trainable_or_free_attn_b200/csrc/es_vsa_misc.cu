@@ -507,7 +507,8 @@ using namespace es::vsa;
 extern "C" int es_vsa_pool(const void* q, const void* k, const void* v, void* qr, void* kr, void* vr, void* qc, void* kc,
                            void* vc, const int32_t* blk_cnt, int32_t BH, int32_t L, int32_t D, int32_t R, int32_t Lr_pad,
                            int32_t NBc_pad, int32_t dtype, void* stream) {
-    if (!q || !k || !blk_cnt) return set_error(-1, "es_vsa_pool: null pointer");
+    if ((!q && !k && !v) || !blk_cnt) return set_error(-1, "es_vsa_pool: null pointer");
+    if ((!q && (qr || qc)) || (!k && (kr || kc))) return set_error(-1, "es_vsa_pool: an output without its input");
     if (int rc = check_shape("es_vsa_pool", BH, L, D, dtype)) return rc;
     if (R < 1 || R > 64 || 64 % R != 0) return set_error(-1, "es_vsa_pool: R must divide 64");
     const int NB = L / TB, G = 64 / R;
@@ -569,6 +570,12 @@ extern "C" long long es_vsa_topk_workspace_bytes(int32_t bh_count, int32_t NB) {
     if (bh_count <= 0 || NB <= 0) return 0;
     const long long W = (NB + 31) / 32;
     return (long long)bh_count * (4 + 4LL * NB + W * NB) * 4;
+}
+
+// Byte offset of the selection bitmap [bh_count, NB, ceil(NB / 32)] that es_vsa_global_topk leaves in its workspace.
+extern "C" long long es_vsa_topk_bits_offset(int32_t bh_count, int32_t NB) {
+    if (bh_count <= 0 || NB <= 0) return 0;
+    return (long long)bh_count * (4 + 4LL * NB) * 4;
 }
 
 extern "C" int es_vsa_global_topk(const float* scores, int32_t NB, int32_t bh0, int32_t bh_count, long long budget,

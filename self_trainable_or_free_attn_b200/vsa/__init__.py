@@ -4,8 +4,10 @@
 package needs neither a GPU nor the native library; the first call loads it and fails loudly when it is missing.
 """
 from .layout import BlockLayout, build_layout, from_blocked, sequence_layout, to_blocked
+from .tiers import RepTiers, TierSelection, rep_fine_attention, route_tiers
 from .ops import (Selection, SplitKV, SplitPolicy, describe_split, fine_block_sparse_attention, mask_to_selection, route,
                   vsa2_attention)
 
 __all__ = ["BlockLayout", "Selection", "build_layout", "fine_block_sparse_attention", "from_blocked", "mask_to_selection",
-           "route", "sequence_layout", "to_blocked", "vsa2_attention", "SplitKV", "SplitPolicy", "describe_split"]
+           "route", "sequence_layout", "to_blocked", "vsa2_attention", "SplitKV", "SplitPolicy", "describe_split", "RepTiers", "TierSelection",
+           "rep_fine_attention", "route_tiers"]

@@ -115,6 +115,23 @@ def main():
         ms_f, _ = timed(lambda: fwd_only(routed), args.repeat)
         ms_fb, _ = timed(lambda: fwd_bwd(routed), args.repeat)
         print(f"  operator, {name:16s} forward {ms_f:8.3f} ms, forward + backward {ms_fb:8.3f} ms")
+    # the 64 / 4 / 1 tiers: tier A = the same budget (topk / NB of the pairs), tier B the next 20 %, tier C the rest
+    from .vsa import tiers as T
+    rt = T.RepTiers(frac_full=args.topk / nb, frac_mid=0.20, mid_reps=4)
+    tsel = T.route_tiers(q, k, cnt, rt, R=16)
+    a_m, b_m, c_m = tsel.tier_masks(nb)
+    na, nbp, ncp = int(a_m.sum()), int(b_m.sum()), int(c_m.sum())
+    flop_t = 4.0 * 64 * 128 * (64 * na + 4 * nbp + ncp)
+    tab = T.rep_build(k, v, cnt, 4)
+    ms_t, (ot, lset) = timed(lambda: T._tier_fwd(q, k, v, tab, tsel, cnt, 4, 7), args.repeat)
+    print(f"  tiers (router selection): pairs A {na}, B {nbp}, C {ncp}; algorithmic {flop_t / 1e12:.3f} TFLOP forward")
+    print(f"  three-tier forward kernel {ms_t:8.3f} ms  {flop_t / ms_t / 1e9:7.1f} TFLOP/s")
+    for ph, name in ((1, "A"), (3, "A+B")):
+        ms_p, _ = timed(lambda: T._tier_fwd(q, k, v, tab, tsel, cnt, 4, ph), args.repeat)
+        print(f"    phases {name:4s}            {ms_p:8.3f} ms")
+    delta_t = (dout.float() * ot.float()).sum(-1)
+    ms_tb, _ = timed(lambda: T._tier_bwd(q, k, v, tab, dout, lset, delta_t, tsel, cnt, 4, 7), args.repeat)
+    print(f"  three-tier backward (dQ pass + tier-A dK/dV + representative pass + unpool) {ms_tb:8.3f} ms")
     print("device status", _native.device_status(), "launches", _native.launch_count())
 
 
