@@ -38,14 +38,16 @@ constexpr int NTHREADS = NSOFT + 96;
 constexpr int MMA_WARP = NSOFT / 32, LOADK_WARP = MMA_WARP + 1, LOADV_WARP = MMA_WARP + 2;
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t O_COL = 256, Q_COL = 384;
-constexpr int NSLOT = 7;      // K / V tiles in flight
+constexpr int NSLOT = 6;      // K / V tiles in flight
+constexpr int NBIAS = 8;      // refine iterations whose column biases are staged in shared memory at a time
 
 constexpr uint32_t TILE_BYTES = 128 * HD * 2;    // 32 KB: [d half][128 rows][64 d], 128B-swizzled
 constexpr uint32_t HALF_BYTES = TILE_BYTES / 2;  // one d half: 128 rows x 128 B
 constexpr uint32_t BLK_BYTES = BK * 128;         // 64 rows of one d half: one TMA box
 constexpr uint32_t SMEM_RING = 0;
 constexpr uint32_t SMEM_CTL = SMEM_RING + NSLOT * TILE_BYTES;
-constexpr uint32_t SMEM_ALLOC = SMEM_CTL + 3072;   // 232,448 B: all of an SM's shared memory
+constexpr uint32_t SMEM_BIAS = SMEM_CTL + 3072;                        // [NBIAS][128] floats
+constexpr uint32_t SMEM_ALLOC = SMEM_BIAS + NBIAS * 128 * 4;           // 203,776 B: one CTA per SM
 
 struct Ctl {
     uint64_t qfull;
@@ -103,23 +105,6 @@ __device__ __forceinline__ void trace_put(uint32_t* tr, int role, int i, int k, 
 __device__ __forceinline__ void trace_put(uint32_t*, int, int, int, long long) {}    // compiled out of release builds
 #endif
 
-// 128 rows x 256 B gathered into one 128B-swizzled tile by the 32 lanes of a warp: list entry e (the block held by lane
-// e in `my`) supplies rows 4e .. 4e+3, which are contiguous in the representative table.
-__device__ __forceinline__ void gather_tile(uint32_t tile, const __nv_bfloat16* table, int my, int lane, uint32_t bar) {
-    const int c16 = lane & 15, kh = c16 >> 3, cc = c16 & 7;
-#pragma unroll 8
-    for (int it = 0; it < 64; ++it) {
-        const int b = __shfl_sync(0xffffffffu, my, it >> 1);
-        const int row = 2 * it + (lane >> 4);
-        const uint32_t dst = tile + (uint32_t)kh * HALF_BYTES + (uint32_t)row * 128 + (uint32_t)((cc ^ (row & 7)) << 4);
-        const char* src = reinterpret_cast<const char*>(table) + ((size_t)(4 * b + (row & 3))) * 256 + c16 * 16;
-        cp_async16(dst, src);
-    }
-    cp_async_mbar_arrive(bar);
-    __syncwarp();
-    if (lane == 0) mbar_arrive(bar);
-}
-
 // p = 2^x for a pair of columns. MUFU computes 16 exponentials per clock and SM, about as many clocks as the tensor
 // cores need for the same tile, so a share of the pairs can be computed on the FMA pipe instead: x = n + f with
 // n = floor(x), 2^f by a degree-4 polynomial (relative error 3e-6, far below the bf16 rounding of P), n added to the
@@ -152,7 +137,8 @@ __device__ __forceinline__ constexpr bool emulate_pair(int j) { return (ES_EMU_P
 template <int MODE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                 const __grid_constant__ CUtensorMap tmKm, const __grid_constant__ CUtensorMap tmVm, const AttnArgs a) {
+                 const __grid_constant__ CUtensorMap tmKm, const __grid_constant__ CUtensorMap tmVm,
+                 const __grid_constant__ CUtensorMap tmKr, const __grid_constant__ CUtensorMap tmVr, const AttnArgs a) {
     constexpr bool FALLBACK = MODE == 1;       // online-softmax recomputation of flagged tiles
     constexpr bool COMPENSATE = MODE == 2;     // block-mean compensation of flagged tiles, added to out / lse in place
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -172,6 +158,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + SMEM_CTL);
     const uint32_t sRing = base + SMEM_RING;
     volatile int* abort_flag = &ctl->abort;
+    float* bias_ring = reinterpret_cast<float*>(smem_raw + SMEM_BIAS);
 
     if (tid == 0) {
         if (base & 1023u) atomicCAS(a.status, 0, 901);   // the swizzled tiles need a 1024-byte aligned base
@@ -222,8 +209,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         bool ok = true;
         const CUtensorMap* map_x = is_v ? &tmV : &tmK;       // exact blocks
         const CUtensorMap* map_m = is_v ? &tmVm : &tmKm;     // block means
-        if (lane == 0) { tma_prefetch_desc(map_x); tma_prefetch_desc(map_m); }
-        const __nv_bfloat16* rep = (is_v ? a.v_rep : a.k_rep) + (size_t)h * a.nb4 * HD;
+        const CUtensorMap* map_r = is_v ? &tmVr : &tmKr;     // representative tables
+        if (lane == 0) { tma_prefetch_desc(map_x); tma_prefetch_desc(map_m); tma_prefetch_desc(map_r); }
         const int* rl = a.refine + (size_t)th_idx * a.rw;
         const uint32_t full0 = smem_u32(&ctl->full[0]), empty0 = smem_u32(&ctl->empty[0]);
         const uint32_t box_off = (uint32_t)(lane >> 1) * HALF_BYTES + (uint32_t)(lane & 1) * BLK_BYTES;   // lanes 0..3
@@ -264,9 +251,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 __syncwarp();
                 if (lane < 4) tma_load_3d(dst + box_off, m, bar, box_x, (lane & 1) ? rb : ra, h);
             } else {
-                // refine iteration: list entry 32 c + e fills columns 4e .. 4e+3 of the 128-column tile
-                const int my = rl[32 * (i - n - nvirt) + lane];
-                gather_tile(dst, rep, my, lane, bar);
+                // refine iteration: list entry 32 c + e (held by lane e) fills rows 4e .. 4e+3 of the tile: the block's four
+                // representatives are contiguous rows of the table, one 512-byte TMA box per d half
+                const int cr = i - n - nvirt;
+                const int my = rl[32 * cr + lane];
+                if (!is_v) {
+                    // the 128 column biases (log2 cluster sizes) of this iteration, for the softmax warps. Slot cr % NBIAS is
+                    // free again: this tile's ring slot was released by QK(i - 3), which was issued after the softmax warps
+                    // had handed over iteration i - 5.
+                    *reinterpret_cast<float4*>(bias_ring + (cr % NBIAS) * 128 + 4 * lane) =
+                        __ldg(reinterpret_cast<const float4*>(a.log_counts + (size_t)h * a.nb4 + 4 * my));
+                    __syncwarp();
+                }
+                if (lane == 0) mbar_arrive_expect_tx(bar, TILE_BYTES);
+                __syncwarp();
+                tma_load_3d(dst + (uint32_t)lane * 512u, map_r, bar, 0, 4 * my, h);
+                tma_load_3d(dst + HALF_BYTES + (uint32_t)lane * 512u, map_r, bar, 64, 4 * my, h);
             }
             pseq = seq + 1;
         };
@@ -308,17 +308,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         const uint32_t sfull0 = smem_u32(&ctl->sfull[0]), pfull0 = smem_u32(&ctl->pfull[0]);
         bool ok = mbar_wait_warp(smem_u32(&ctl->qfull), 0, abort_flag, a.status, 201);     // Q is in tensor memory
         // next tile of the ring: returns its slot
-        auto take = [&](bool gathered) -> uint32_t {
+        auto take = [&]() -> uint32_t {
             const uint32_t slot = cslot;
             ok = ok && mbar_wait_warp(full0 + 8 * slot, cpar, abort_flag, a.status, 202);
             if (++cslot == NSLOT) { cslot = 0; cpar ^= 1; }
-            if (gathered) fence_proxy_async_smem();    // cp.async gathers are generic-proxy writes
             return slot;
         };
         // S[buf] <- Q K^T. The S columns also hold the previous P of that buffer: every earlier use must have been handed
         // back by the softmax warps (pfull) before they are overwritten; the PV that read it was issued before (in order).
-        auto issue_qk = [&](int buf, bool gathered, int ti = TRACE_ITERS) {
-            const uint32_t slot = take(gathered);
+        auto issue_qk = [&](int buf, int ti = TRACE_ITERS) {
+            const uint32_t slot = take();
             if (lane == 0) trace_put(a.trace, 1, ti, 5, t_start);
             while (ok && wP[buf] < nQK[buf]) {
                 ok = mbar_wait_warp(pfull0 + 8 * buf, wP[buf] & 1, abort_flag, a.status, 203);
@@ -340,14 +339,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             ++nQK[buf];
         };
         if (FALLBACK) {
-            for (int i = 0; i < n && ok; ++i) issue_qk(i & 1, false);
+            for (int i = 0; i < n && ok; ++i) issue_qk(i & 1);
         }
-        if (nt > 0) issue_qk(0, n + nvirt == 0);
-        if (nt > 1) issue_qk(1, n + nvirt <= 1);
+        if (nt > 0) issue_qk(0);
+        if (nt > 1) issue_qk(1);
         for (int i = 0; i < nt && ok; ++i) {
             const int buf = i & 1;
             if (lane == 0) trace_put(a.trace, 1, i, 0, t_start);
-            const uint32_t slot = take(i >= n + nvirt);
+            const uint32_t slot = take();
             if (lane == 0) trace_put(a.trace, 1, i, 1, t_start);
             ok = ok && mbar_wait_warp(pfull0 + 8 * buf, wP[buf] & 1, abort_flag, a.status, 205);   // P(i) stored
             if (lane == 0) trace_put(a.trace, 1, i, 2, t_start);
@@ -367,7 +366,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             }
             __syncwarp();
             if (lane == 0) trace_put(a.trace, 1, i, 3, t_start);
-            if (i + 2 < nt) issue_qk(buf, i + 2 >= n + nvirt, i);
+            if (i + 2 < nt) issue_qk(buf, i);
             if (lane == 0) trace_put(a.trace, 1, i, 4, t_start);
         }
         // every MMA issued above has finished before tensor memory is freed
@@ -429,8 +428,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         }
 
         float2 lsum = make_float2(0.f, 0.f);
-        const int* rl = a.refine + (size_t)th_idx * a.rw;
-        const float* lc = a.log_counts + (size_t)h * a.nb4;
         const int* bits = a.skip_bits + ((size_t)h * a.nq + qb) * a.nw;
         const bool want_mass = !FALLBACK && !COMPENSATE && a.mass != nullptr;
         const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
@@ -462,6 +459,12 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 nblk = list[e < n64 ? e : e - 1];
             }
             flush_mass();
+            // the skip words of a block-mean iteration are fetched before the wait, so that their latency is hidden by it
+            uint32_t w0 = 0, w1 = 0;
+            if (pooled && !COMPENSATE) {
+                w0 = (uint32_t)__ldg(bits + 4 * (i - n) + 2 * ch);
+                w1 = (uint32_t)__ldg(bits + 4 * (i - n) + 2 * ch + 1);
+            }
             if (tid == 0) trace_put(a.trace, 0, i, 0, t_start);
             ok = ok && mbar_wait_warp(smem_u32(&ctl->sfull[buf]), uS[buf] & 1, abort_flag, a.status, 302);
             if (!ok) break;
@@ -501,7 +504,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             } else if (pooled) {
                 // block-mean columns: column c of this half is block 128 cv + 64 ch + c; a set bit masks it
                 const int cv = i - n;
-                uint32_t w0, w1;
                 if (COMPENSATE) {
                     // every block that was not kept (refined ones included) is compensated: bits from the keep mask
                     const int b0 = 128 * cv + 64 * ch;
@@ -512,9 +514,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                         w0 |= (uint32_t)(b0 + c >= a.nb ? 1 : kp[c] != 0) << c;
                         w1 |= (uint32_t)(b0 + 32 + c >= a.nb ? 1 : kp[32 + c] != 0) << c;
                     }
-                } else {
-                    w0 = (uint32_t)bits[4 * cv + 2 * ch];
-                    w1 = (uint32_t)bits[4 * cv + 2 * ch + 1];
                 }
                 const float2 off2 = make_float2(-m + 6.0f, -m + 6.0f);   // log2(64): a mean stands for its block's tokens
                 const int last_c = (a.nb - 1) - (128 * cv + 64 * ch);    // column of the (maybe shorter) last block
@@ -533,27 +532,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                     pk[j] = pack_bf16x2(p.x, p.y);
                 }
             } else {
-                // representatives: columns 4e .. 4e+3 of this half belong to list entry 32 cr + 16 ch + e
+                // representatives: column c of this half has the bias that the K load warp staged for this iteration
                 const int cr = i - n - nvirt;
-                const int4* ent = reinterpret_cast<const int4*>(rl + 32 * cr + 16 * ch);
+                const float4* bb = reinterpret_cast<const float4*>(bias_ring + (cr % NBIAS) * 128 + 64 * ch);
 #pragma unroll
-                for (int e4 = 0; e4 < 4; ++e4) {
-                    const int4 bq = __ldg(ent + e4);
-                    const int bl[4] = {bq.x, bq.y, bq.z, bq.w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const float4 b4 = __ldg(reinterpret_cast<const float4*>(lc + 4 * bl[j]));
-                        const int c = 16 * e4 + 4 * j;
-                        const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2,
-                                                     make_float2(b4.x - m, b4.y - m));
-                        const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), sc2,
-                                                     make_float2(b4.z - m, b4.w - m));
-                        const float2 p0 = exp2_pair_mufu(x0), p1 = exp2_pair_mufu(x1);
-                        acc = __fadd2_rn(acc, p0);
-                        acc1 = __fadd2_rn(acc1, p1);
-                        pk[c / 2] = pack_bf16x2(p0.x, p0.y);
-                        pk[c / 2 + 1] = pack_bf16x2(p1.x, p1.y);
-                    }
+                for (int e = 0; e < 16; ++e) {
+                    const float4 b4 = bb[e];
+                    const int c = 4 * e;
+                    const float2 x0 = __ffma2_rn(make_float2(__uint_as_float(s[c]), __uint_as_float(s[c + 1])), sc2,
+                                                 make_float2(b4.x - m, b4.y - m));
+                    const float2 x1 = __ffma2_rn(make_float2(__uint_as_float(s[c + 2]), __uint_as_float(s[c + 3])), sc2,
+                                                 make_float2(b4.z - m, b4.w - m));
+                    const float2 p0 = exp2_pair_mufu(x0), p1 = exp2_pair_mufu(x1);
+                    acc = __fadd2_rn(acc, p0);
+                    acc1 = __fadd2_rn(acc1, p1);
+                    pk[c / 2] = pack_bf16x2(p0.x, p0.y);
+                    pk[c / 2 + 1] = pack_bf16x2(p1.x, p1.y);
                 }
             }
             if (tid == 0) trace_put(a.trace, 0, i, 3, t_start);
@@ -669,6 +663,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 }
 
 // ---------------------------------------------------------------------------------------------- host side
+// Representative tables (H, rows, 128) bf16 viewed as dims {128 d, rows, H}; a box is 64 d x 4 rows (one block's four rows).
+static int make_rep_map(CUtensorMap* m, const void* ptr, int rows, int H) {
+    cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)rows, (cuuint64_t)H};
+    cuuint64_t strides[2] = {(cuuint64_t)HD * 2, (cuuint64_t)rows * HD * 2};
+    cuuint32_t box[3] = {64, 4, 1};
+    cuuint32_t estr[3] = {1, 1, 1};
+    return encode_tensor_map(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 static int make_map(CUtensorMap* m, const void* ptr, int rows, int H, int box_rows) {
     // (rows, H, 128) bf16 viewed as dims {128 d, rows, H}; a box is 64 d x box_rows rows, 128-byte swizzled
     cuuint64_t dims[3] = {(cuuint64_t)HD, (cuuint64_t)rows, (cuuint64_t)H};
@@ -691,7 +695,7 @@ static int launch_attention(const AttnCall& c, int mode, cudaStream_t stream) {
     if (a.L <= 0 || a.H <= 0) return set_error(-1, "attention: L and H must be positive");
     if (((uintptr_t)c.q | (uintptr_t)c.k | (uintptr_t)c.v | (uintptr_t)a.out) & 15)
         return set_error(-1, "attention: q, k, v, out must be 16-byte aligned");
-    CUtensorMap tk, tv, tkm, tvm;
+    CUtensorMap tk, tv, tkm, tvm, tkr, tvr;
     int rc;
     if ((rc = make_map(&tk, c.k, a.L, a.H, BK))) return rc;
     if ((rc = make_map(&tv, c.v, a.L, a.H, BK))) return rc;
@@ -701,6 +705,13 @@ static int launch_attention(const AttnCall& c, int mode, cudaStream_t stream) {
     } else {
         tkm = tk; tvm = tv;
     }
+    if (a.nref > 0) {
+        if (((uintptr_t)a.k_rep | (uintptr_t)a.v_rep) & 15) return set_error(-1, "attention: k_rep, v_rep must be 16-byte aligned");
+        if ((rc = make_rep_map(&tkr, a.k_rep, a.nb4, a.H))) return rc;
+        if ((rc = make_rep_map(&tvr, a.v_rep, a.nb4, a.H))) return rc;
+    } else {
+        tkr = tk; tvr = tv;
+    }
     static bool attr_set[3] = {false, false, false};
     auto kern = mode == 0 ? attention_kernel<0> : mode == 1 ? attention_kernel<1> : attention_kernel<2>;
     if (!attr_set[mode]) {
@@ -708,7 +719,7 @@ static int launch_attention(const AttnCall& c, int mode, cudaStream_t stream) {
         if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
         attr_set[mode] = true;
     }
-    kern<<<a.nq * a.H, NTHREADS, SMEM_ALLOC, stream>>>(tk, tv, tkm, tvm, a);
+    kern<<<a.nq * a.H, NTHREADS, SMEM_ALLOC, stream>>>(tk, tv, tkm, tvm, tkr, tvr, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
     count_launch();
