@@ -134,6 +134,23 @@ __device__ __forceinline__ float2 exp2_pair_fma(float2 x) {
 #endif
 __device__ __forceinline__ constexpr bool emulate_pair(int j) { return (ES_EMU_PATTERN >> (j & 7)) & 1; }
 
+// Order of a tile's iterations. The refine iterations (64 small TMA boxes per tile, slow to fill) are spread evenly among
+// the others instead of coming last, so that the ring refills during the cheap iterations in between: iteration i is the
+// refine iteration i / p when i % p == p - 1 and i / p < nref (p = nt / nref); the other iterations are the exact ones,
+// then the block-mean ones, in their order. kind: 0 exact, 1 block means, 2 refine; idx counts within the kind.
+struct Sched {
+    int n, nvirt, nref, p;
+    __device__ __forceinline__ void decode(int i, int& kind, int& idx) const {
+        if (nref > 0) {
+            const int q = i / p;
+            if (i - q * p == p - 1 && q < nref) { kind = 2; idx = q; return; }
+            i -= min(q, nref);
+        }
+        if (i < n) { kind = 0; idx = i; }
+        else { kind = 1; idx = i - n; }
+    }
+};
+
 template <int MODE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -197,6 +214,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     const int nref = (FALLBACK || COMPENSATE) ? 0 : a.nref;
     const int nt = n + nvirt + nref;
     const int* list = a.blocks + (size_t)th_idx * a.nk;
+    const Sched sched{n, nvirt, nref, nref > 0 ? max(nt / nref, 1) : 1};
 
     // K and V tiles travel through one ring of NSLOT slots in the order the MMA warp consumes them:
     //   [fallback sweep: K(0) K(1) ... K(n-1)]  K(0) K(1)  { V(i) K(i+2) } for i = 0 .. nt-1
@@ -222,8 +240,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             if (!ok) return;
             int ra = 0, rb = 64;
             const CUtensorMap* m = map_m;
-            if (i < n) {
-                const int e = 2 * i;
+            int kind, idx;
+            if (i < 0) { kind = 0; idx = -i - 1; }        // a K tile of the fallback sweep
+            else sched.decode(i, kind, idx);
+            if (kind == 0) {
+                const int e = 2 * idx;
                 if ((e & ~31) != wbase) {
                     wbase = e & ~31;
                     win = (wbase + lane < n64) ? list[wbase + lane] : 0;
@@ -233,7 +254,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 if (e + 1 >= n64) rb = ra;                     // odd list: block a again, masked in the softmax
                 m = map_x;
             } else {
-                ra = (i - n) * 128;                            // rows of the block-mean tables
+                ra = idx * 128;                                // rows of the block-mean tables
                 rb = ra + 64;
             }
             const uint32_t slot = seq % NSLOT, par = ((seq / NSLOT) & 1) ^ 1;
@@ -246,14 +267,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 if (lane == 0) mbar_arrive(bar);
             } else
 #endif
-            if (i < n + nvirt) {
+            if (kind != 2) {
                 if (lane == 0) mbar_arrive_expect_tx(bar, TILE_BYTES);
                 __syncwarp();
                 if (lane < 4) tma_load_3d(dst + box_off, m, bar, box_x, (lane & 1) ? rb : ra, h);
             } else {
                 // refine iteration: list entry 32 c + e (held by lane e) fills rows 4e .. 4e+3 of the tile: the block's four
                 // representatives are contiguous rows of the table, one 512-byte TMA box per d half
-                const int cr = i - n - nvirt;
+                const int cr = idx;
                 const int my = rl[32 * cr + lane];
                 if (!is_v) {
                     // the 128 column biases (log2 cluster sizes) of this iteration, for the softmax warps. Slot cr % NBIAS is
@@ -276,7 +297,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             // rounds apart (one parity bit), so the V warp must not start polling while the ring is still rounds behind
             // its first tile: it starts once the K warp has issued the last sweep tile.
             if (!is_v) {
-                for (int i = 0; i < n; ++i) put((uint32_t)i, i);
+                for (int i = 0; i < n; ++i) put((uint32_t)i, -i - 1);
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->sweepbar));
             } else {
                 if (lane == 0) ok = mbar_wait(smem_u32(&ctl->sweepbar), 0, abort_flag, a.status, 102);
@@ -431,8 +452,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         const int* bits = a.skip_bits + ((size_t)h * a.nq + qb) * a.nw;
         const bool want_mass = !FALLBACK && !COMPENSATE && a.mass != nullptr;
         const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
-        // block id of this warp's column half in the exact iteration that comes next, loaded one iteration ahead
-        int nblk = n > 0 ? list[ch < n64 ? ch : 0] : 0;
         // thread 0 stores the masses of an iteration at the start of the next one: by then the other warps' partial sums
         // have long arrived, so the store never holds back the warp that the others wait for
         int pend_a = -1, pend_b = -1, pend_i = 0;
@@ -451,19 +470,18 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         };
         for (int i = 0; i < nt && ok; ++i) {
             const int buf = i & 1;
-            const bool exact = i < n, pooled = !exact && i < n + nvirt;
-            const int blk = nblk;
-            const bool has = !exact || 2 * i + ch < n64;
-            if (i + 1 < n) {
-                const int e = 2 * i + 2 + ch;
-                nblk = list[e < n64 ? e : e - 1];
-            }
+            int kind, idx;
+            sched.decode(i, kind, idx);
+            const bool exact = kind == 0, pooled = kind == 1;
+            const bool has = !exact || 2 * idx + ch < n64;
+            // block id of this warp's column half, fetched before the wait
+            const int blk = exact ? __ldg(list + (has ? 2 * idx + ch : 2 * idx + ch - 1)) : 0;
             flush_mass();
             // the skip words of a block-mean iteration are fetched before the wait, so that their latency is hidden by it
             uint32_t w0 = 0, w1 = 0;
             if (pooled && !COMPENSATE) {
-                w0 = (uint32_t)__ldg(bits + 4 * (i - n) + 2 * ch);
-                w1 = (uint32_t)__ldg(bits + 4 * (i - n) + 2 * ch + 1);
+                w0 = (uint32_t)__ldg(bits + 4 * idx + 2 * ch);
+                w1 = (uint32_t)__ldg(bits + 4 * idx + 2 * ch + 1);
             }
             if (tid == 0) trace_put(a.trace, 0, i, 0, t_start);
             ok = ok && mbar_wait_warp(smem_u32(&ctl->sfull[buf]), uS[buf] & 1, abort_flag, a.status, 302);
@@ -503,7 +521,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 }
             } else if (pooled) {
                 // block-mean columns: column c of this half is block 128 cv + 64 ch + c; a set bit masks it
-                const int cv = i - n;
+                const int cv = idx;
                 if (COMPENSATE) {
                     // every block that was not kept (refined ones included) is compensated: bits from the keep mask
                     const int b0 = 128 * cv + 64 * ch;
@@ -533,7 +551,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 }
             } else {
                 // representatives: column c of this half has the bias that the K load warp staged for this iteration
-                const int cr = i - n - nvirt;
+                const int cr = idx;
                 const float4* bb = reinterpret_cast<const float4*>(bias_ring + (cr % NBIAS) * 128 + 64 * ch);
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
@@ -568,13 +586,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) pa += __shfl_xor_sync(0xffffffffu, pa, o);
                 if (lane == 0) {
-                    ctl->mass_part[i & 3][ch][rq] = pa;
-                    mbar_arrive(smem_u32(&ctl->massbar[i & 3]));
+                    ctl->mass_part[idx & 3][ch][rq] = pa;
+                    mbar_arrive(smem_u32(&ctl->massbar[idx & 3]));
                 }
                 if (tid == 0) {
                     pend_a = blk;
-                    pend_b = (2 * i + 1 < n64) ? list[2 * i + 1] : -1;
-                    pend_i = i;
+                    pend_b = (2 * idx + 1 < n64) ? list[2 * idx + 1] : -1;
+                    pend_i = idx;                      // slots and barrier phases count the exact iterations
                 }
             }
         }
