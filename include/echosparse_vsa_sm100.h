@@ -53,6 +53,19 @@ int es_vsa_global_topk(const float* scores, int32_t NB, int32_t bh0, int32_t bh_
  * experiments/vsa2_representative/csrc/rep/rep_api.cpp:90-170 `route_tiers`, which runs the same top-k at two budgets). */
 long long es_vsa_topk_bits_offset(int32_t bh_count, int32_t NB);
 
+/* Original-VSA router, stage 1: whole-block scores [bh_count, NB, NB] in the element type, S = rnd(rnd(qc . kc) * (1 / sqrt(D))),
+ * rnd = round to the element type (what Torch's bf16 / fp16 `(q_c @ k_c^T) / sqrt(D)` computes).
+ * Replaces `block_scores` (launch_block_scores, csrc/vsa/vsa2_kernels.h:253). */
+int es_vsa_block_scores(const void* qc, const void* kc, void* scores, int32_t BH, int32_t NB, int32_t D, int32_t NBc_pad,
+                        int32_t bh0, int32_t bh_count, int32_t dtype, void* stream);
+
+/* Original-VSA router, stage 2: exactly K = min(topk, NB) kv blocks per query row, larger score first, ties to the smaller kv
+ * index, -0 == +0; q -> kv lists (row r of head bh owns idx[(bh * NB + r) * K ..)) and their inverse. The workspace is
+ * es_vsa_topk_workspace_bytes(bh_count, NB) bytes. Replaces `row_topk_into` / `route_rows` (launch_row_topk,
+ * csrc/vsa/vsa2_kernels.h:270). */
+int es_vsa_row_topk(const void* scores, int32_t NB, int32_t bh0, int32_t bh_count, int32_t topk, int32_t* q2k_ptr,
+                    int32_t* q2k_idx, int32_t* k2q_ptr, int32_t* k2q_idx, void* workspace, int32_t dtype, void* stream);
+
 /* Attention of every 64-row query block over the valid tokens of its listed kv blocks (online softmax): o [BH, L, D],
  * lse [BH, L]. Also the coarse branch (block means as a sequence, 64-row tiles with their own counts, dense lists).
  * Replaces `attn_fwd` (launch_attn_fwd, csrc/vsa/vsa2_kernels.h:146). */

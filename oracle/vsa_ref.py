@@ -226,3 +226,31 @@ def split_plan(ptr, chunk, max_slots, min_len=0, rel_mean=0.0, tail_frac=0.0, re
     t_split = slot
     tasks += [[int(r), int(beg[r]), int(beg[r] + n[r]), -1] for r in np.nonzero(~split)[0]]
     return tasks, merges, [len(tasks), len(merges), t_split, BH * nb, E, int(E <= budget), gthr, W]
+
+
+# ------------------------------------------------------------------------------------------- original VSA
+def vsa_block_scores(q, k, blk_cnt):
+    """Whole-block router scores of the original VSA in the token dtype (reference: tests/vsa_reference.py:147-160, the
+    kernel's rounding csrc/vsa/vsa2_kernels.h:243-253): block means rounded to the dtype, fp32 dot rounded once, times the
+    fp32 reciprocal of sqrt(D), rounded again."""
+    dt = q.dtype
+    qc = block_means(q.float(), blk_cnt, dt)
+    kc = block_means(k.float(), blk_cnt, dt)
+    once = (qc @ kc.transpose(-1, -2)).to(dt).float()
+    inv = torch.tensor(1.0, dtype=torch.float32) / torch.tensor(float(q.shape[-1]) ** 0.5, dtype=torch.float32)
+    return (once * inv).to(dt)
+
+
+def row_topk_mask(scores, topk):
+    """Exactly min(topk, NB) kv blocks per row: score descending, ties to the smaller kv index, -0 == +0
+    (reference: tests/vsa_reference.py:163-168)."""
+    n = max(0, min(int(topk), scores.shape[-1]))
+    order = torch.sort(scores.float() + 0.0, dim=-1, descending=True, stable=True).indices[..., :n]
+    return torch.zeros(scores.shape, dtype=torch.bool).scatter_(-1, order, True)
+
+
+def vsa_output(q, k, v, weight, blk_cnt, mask):
+    """Original VSA on a frozen mask: O = O_fine + W * O_coarse[block], W a full [B,H,L,D] weight or None (1). The same
+    arithmetic as `vsa2_output` with an identity gate per element (reference: tests/vsa_reference.py:171-193 states it with
+    the original's extra rounding points; its own test tests/test_vsa.py:87-107 shows both agree without rounding)."""
+    return vsa2_output(q, k, v, weight, blk_cnt, mask, gate_act="identity")

@@ -57,6 +57,8 @@ SIGNATURES = {
     "es_vsa_attn_bwd_q_tasks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _P],
     "es_vsa_split_merge_sum": [_P, _P, _P, _I, _P, _I, _P, _P, _P, _I, _I, _I, _P],
     "es_vsa_topk_bits_offset": [_I, _I],
+    "es_vsa_block_scores": [_P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
+    "es_vsa_row_topk": [_P, _I, _I, _I, _I, _P, _P, _P, _P, _P, _I, _P],
     "es_vsa_tier_attn_fwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "es_vsa_tier_attn_bwd_q": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I,
                                _I, _I, _I, _P],

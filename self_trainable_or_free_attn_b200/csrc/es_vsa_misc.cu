@@ -366,6 +366,123 @@ __global__ void __launch_bounds__(128) topk_cols_kernel(const TopkArgs a, int pa
     }
 }
 
+// ---------------------------------------------------------------------------------------------- original-VSA router
+// Whole-block scores in the original's rounding (reference: BlockScoreParams, csrc/vsa/vsa2_kernels.h:243-253):
+// S = rnd(rnd(qc . kc) * scale), rnd = round to the element type, scale = the fp32 reciprocal of sqrt(D): what Torch's
+// `(q_c @ k_c^T) / sqrt(D)` computes in bf16 / fp16 (fp32-accumulated product rounded once, then multiplied by the fp32
+// reciprocal of the scalar and rounded again). One thread per score; the means are small and stay in cache.
+struct BlockScoreArgs {
+    const void *qc, *kc;
+    void* scores;            // [bh_count, NB, NB] element type
+    int NB, NBc_pad, bh0;
+    float inv_scale;
+};
+template <typename T, int D>
+__global__ void __launch_bounds__(128) block_scores_kernel(const BlockScoreArgs a) {
+    const int j = blockIdx.x * 128 + threadIdx.x, i = blockIdx.y, b = blockIdx.z, bh = a.bh0 + b;
+    if (j >= a.NB) return;
+    const T* q = static_cast<const T*>(a.qc) + ((size_t)bh * a.NBc_pad + i) * D;
+    const T* k = static_cast<const T*>(a.kc) + ((size_t)bh * a.NBc_pad + j) * D;
+    float acc = 0.f;
+#pragma unroll 8
+    for (int d = 0; d < D; d += 2) {
+        const float2 x = Elt<T>::unpack(*reinterpret_cast<const uint32_t*>(q + d));
+        const float2 y = Elt<T>::unpack(*reinterpret_cast<const uint32_t*>(k + d));
+        acc = fmaf(x.x, y.x, acc);
+        acc = fmaf(x.y, y.y, acc);
+    }
+    const float once = Elt<T>::to_float(Elt<T>::from_float(acc));
+    static_cast<T*>(a.scores)[((size_t)b * a.NB + i) * a.NB + j] = Elt<T>::from_float(once * a.inv_scale);
+}
+
+// Per query row: exactly K = min(topk, NB) kv blocks, larger score first, ties to the smaller kv index, -0 == +0
+// (reference: RowTopkParams, csrc/vsa/vsa2_kernels.h:255-270). One CTA per row: two-pass radix select of the K-th largest
+// 16-bit key, then the ascending list and the selection bits. Row r of (b, h) owns idx[((b, h) * NB + r) * K ..).
+struct RowTopkArgs {
+    const uint16_t* scores;  // [bh_count, NB, NB]
+    int NB, W, bh0, K, fp16;
+    int *q2k_ptr, *q2k_idx;
+    uint32_t* selbits;       // [bh_count, NB, W]
+};
+__device__ __forceinline__ uint32_t key16(uint16_t u, int fp16) {
+    // bf16 and fp16 order like their bit patterns once the sign is handled; -0 becomes +0
+    if ((u & 0x7FFFu) == 0) u = 0;
+    (void)fp16;
+    return (u & 0x8000u) ? (uint32_t)(uint16_t)~u : (uint32_t)(u | 0x8000u);
+}
+__global__ void __launch_bounds__(128) row_topk_kernel(const RowTopkArgs a) {
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t s_prefix, s_need;
+    __shared__ int warp_gt[4], warp_eq[4];
+    const int row = blockIdx.x, b = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, bh = a.bh0 + b;
+    const uint16_t* sc = a.scores + ((size_t)b * a.NB + row) * a.NB;
+    const long long base = ((long long)bh * a.NB + row) * a.K;
+    if (tid == 0) {
+        a.q2k_ptr[(size_t)bh * (a.NB + 1) + row] = (int)base;
+        if (row == a.NB - 1) a.q2k_ptr[(size_t)bh * (a.NB + 1) + a.NB] = (int)(base + a.K);
+        s_prefix = 0; s_need = (uint32_t)a.K;
+    }
+    __syncthreads();
+    uint32_t thr = 0xFFFFFFFFu;
+    int need = 0;
+    if (a.K > 0) {
+        for (int pass = 0; pass < 2; ++pass) {
+            const int shift = 8 - 8 * pass;
+            for (int x = tid; x < 256; x += 128) hist[x] = 0;
+            __syncthreads();
+            const uint32_t prefix = s_prefix, mask = pass == 0 ? 0u : 0xFF00u;
+            for (int j = tid; j < a.NB; j += 128) {
+                const uint32_t key = key16(sc[j], a.fp16);
+                if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255], 1u);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                uint32_t nd = s_need, d = 255;
+                for (;; --d) {
+                    if (hist[d] >= nd) break;
+                    nd -= hist[d];
+                    if (d == 0) break;
+                }
+                s_prefix = prefix | (d << shift);
+                s_need = nd;
+            }
+            __syncthreads();
+        }
+        thr = s_prefix; need = (int)s_need;
+    }
+    // ascending emission, 128 columns at a time
+    int pos = 0, eqrank = 0;
+    for (int j0 = 0; j0 < a.NB; j0 += 128) {
+        const int j = j0 + tid;
+        const uint32_t key = j < a.NB ? key16(sc[j], a.fp16) : 0u;
+        const bool gt = j < a.NB && a.K > 0 && key > thr, eq = j < a.NB && a.K > 0 && key == thr;
+        const unsigned gm = __ballot_sync(0xffffffffu, gt), em = __ballot_sync(0xffffffffu, eq);
+        if (lane == 0) { warp_gt[warp] = __popc(gm); warp_eq[warp] = __popc(em); }
+        __syncthreads();
+        int eq_before = eqrank, take_before = 0;
+        for (int w = 0; w < warp; ++w) eq_before += warp_eq[w];
+        const int my_eq = eq_before + __popc(em & ((1u << lane) - 1));
+        const bool take = gt || (eq && my_eq < need);
+        const unsigned tm = __ballot_sync(0xffffffffu, take);
+        // positions: takes of the earlier warps of this chunk = their gt + their eq clipped to the remaining need
+        int run_eq = eqrank;
+        for (int w = 0; w < warp; ++w) {
+            take_before += warp_gt[w] + max(0, min(warp_eq[w], need - run_eq));
+            run_eq += warp_eq[w];
+        }
+        if (take) a.q2k_idx[base + pos + take_before + __popc(tm & ((1u << lane) - 1))] = j;
+        if (lane == 0 && j0 + 32 * warp < a.W * 32) a.selbits[((size_t)b * a.NB + row) * a.W + (j0 >> 5) + warp] = tm;
+        int chunk_take = 0, chunk_eq = 0, r2 = eqrank;
+        for (int w = 0; w < 4; ++w) {
+            chunk_take += warp_gt[w] + max(0, min(warp_eq[w], need - r2));
+            r2 += warp_eq[w];
+            chunk_eq += warp_eq[w];
+        }
+        pos += chunk_take; eqrank += chunk_eq;
+        __syncthreads();
+    }
+}
+
 // ---------------------------------------------------------------------------------------------- gate fusion
 // gate_mode: 0 none (weight 1), 1 one value per token [BH, L], 2 one per element [BH, L, D]; gate_act: 0 tanh, 1 identity.
 struct FuseArgs {
@@ -661,5 +778,51 @@ extern "C" int es_vsa_finalize(const float* acc, const float* add, void* out, co
     const dim3 grid(L / TB, BH);
     VSA_LAUNCH(finalize_kernel, grid, D / 2, 0, a);
     ES_CHECK_LAUNCH("finalize_kernel");
+    return 0;
+}
+
+extern "C" int es_vsa_block_scores(const void* qc, const void* kc, void* scores, int32_t BH, int32_t NB, int32_t D,
+                                   int32_t NBc_pad, int32_t bh0, int32_t bh_count, int32_t dtype, void* stream) {
+    if (!qc || !kc || !scores) return set_error(-1, "es_vsa_block_scores: null pointer");
+    if (int rc = check_shape("es_vsa_block_scores", BH, NB * TB, D, dtype)) return rc;
+    if (NBc_pad < NB || bh0 < 0 || bh_count < 1 || bh0 + bh_count > BH) return set_error(-1, "es_vsa_block_scores: bad sizes");
+    BlockScoreArgs a{qc, kc, scores, NB, NBc_pad, bh0, 1.0f / sqrtf((float)D)};
+    cudaStream_t st = (cudaStream_t)stream;
+    const dim3 grid((NB + 127) / 128, NB, bh_count);
+    VSA_LAUNCH(block_scores_kernel, grid, 128, 0, a);
+    ES_CHECK_LAUNCH("block_scores_kernel");
+    return 0;
+}
+
+extern "C" int es_vsa_row_topk(const void* scores, int32_t NB, int32_t bh0, int32_t bh_count, int32_t topk,
+                               int32_t* q2k_ptr, int32_t* q2k_idx, int32_t* k2q_ptr, int32_t* k2q_idx, void* workspace,
+                               int32_t dtype, void* stream) {
+    if (!scores || !q2k_ptr || !q2k_idx || !k2q_ptr || !k2q_idx || !workspace) return set_error(-1, "es_vsa_row_topk: null pointer");
+    if (NB <= 0 || bh_count <= 0 || bh0 < 0 || topk < 0) return set_error(-1, "es_vsa_row_topk: bad sizes");
+    if (dtype != 0 && dtype != 1) return set_error(-1, "es_vsa_row_topk: dtype must be 0 (bf16) or 1 (fp16)");
+    const int K = topk < NB ? topk : NB;
+    if ((long long)(bh0 + bh_count) * NB * K > 0x7FFFFFFFLL) return set_error(-1, "es_vsa_row_topk: offsets exceed int32");
+    // the workspace has the layout of es_vsa_global_topk's: the column stages are shared with it
+    TopkArgs t{};
+    t.NB = NB; t.W = (NB + 31) / 32; t.bh0 = bh0; t.budget = (long long)NB * K;
+    t.q2k_ptr = q2k_ptr; t.q2k_idx = q2k_idx; t.k2q_ptr = k2q_ptr; t.k2q_idx = k2q_idx;
+    int* w = static_cast<int*>(workspace);
+    t.state = w; w += (size_t)bh_count * 4;
+    t.gtcnt = w; w += (size_t)bh_count * NB;
+    t.eqcnt = w; w += (size_t)bh_count * NB;
+    t.eqbase = w; w += (size_t)bh_count * NB;
+    t.colcnt = w; w += (size_t)bh_count * NB;
+    t.selbits = reinterpret_cast<uint32_t*>(w);
+    RowTopkArgs a{static_cast<const uint16_t*>(scores), NB, t.W, bh0, K, dtype, q2k_ptr, q2k_idx, t.selbits};
+    cudaStream_t st = (cudaStream_t)stream;
+    row_topk_kernel<<<dim3(NB, bh_count), 128, 0, st>>>(a);
+    ES_CHECK_LAUNCH("row_topk_kernel");
+    const dim3 cols((NB + 127) / 128, bh_count);
+    topk_cols_kernel<<<cols, 128, 0, st>>>(t, 0);
+    ES_CHECK_LAUNCH("topk_cols_kernel");
+    topk_scan_kernel<<<bh_count, 1024, 0, st>>>(t, 1);
+    ES_CHECK_LAUNCH("topk_scan_kernel");
+    topk_cols_kernel<<<cols, 128, 0, st>>>(t, 1);
+    ES_CHECK_LAUNCH("topk_cols_kernel");
     return 0;
 }

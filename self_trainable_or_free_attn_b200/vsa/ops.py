@@ -150,6 +150,41 @@ def route(q, k, blk_cnt, R=16, topk=None, budget=None, row_norm="paper"):
     return _route(qr, kr, blk_cnt, R, budget_from_topk(q.shape[2] // 64, topk, budget), ROW_NORMS[row_norm])
 
 
+# Original VSA only needs the whole-block means of pool_fwd; R = 32 makes its unused router pools smallest.
+_ROWS_POOL_R = 32
+
+
+def block_scores(qc, kc, nb):
+    """Original-VSA block scores [B, H, NB, NB] in the token dtype from the block means."""
+    B, H, nbc_pad, D = qc.shape
+    scores = torch.empty(B, H, nb, nb, device=qc.device, dtype=qc.dtype)
+    N.check(N.load().es_vsa_block_scores(N.ptr(qc), N.ptr(kc), N.ptr(scores), B * H, nb, D, nbc_pad, 0, B * H,
+                                         _DTYPES[qc.dtype], N.stream_ptr()), "es_vsa_block_scores")
+    return scores
+
+
+def row_topk(scores, topk):
+    """Exactly min(topk, NB) kv blocks per query row of 16-bit scores [B, H, NB, NB] -> Selection."""
+    B, H, nb, _ = scores.shape
+    K = max(0, min(int(topk), nb))
+    lib = N.load()
+    i32 = dict(device=scores.device, dtype=torch.int32)
+    qp, kp = torch.empty(B, H, nb + 1, **i32), torch.empty(B, H, nb + 1, **i32)
+    qi, ki = torch.empty(max(1, B * H * nb * K), **i32), torch.empty(max(1, B * H * nb * K), **i32)
+    ws = torch.empty(int(lib.es_vsa_topk_workspace_bytes(B * H, nb)), device=scores.device, dtype=torch.uint8)
+    N.check(lib.es_vsa_row_topk(N.ptr(scores.contiguous()), nb, 0, B * H, K, N.ptr(qp), N.ptr(qi), N.ptr(kp), N.ptr(ki),
+                                N.ptr(ws), _DTYPES[scores.dtype], N.stream_ptr()), "es_vsa_row_topk")
+    return Selection(qp, qi, kp, ki)
+
+
+def route_rows(q, k, blk_cnt, topk):
+    """Standalone original-VSA router (stop-gradient): whole-block scores, exactly min(topk, NB) blocks per row."""
+    _check_tokens(q, k, k)
+    blk_cnt = blk_cnt.to(torch.int32).contiguous()
+    _, _, qc, kc, _ = pool_fwd(q, k, k, blk_cnt, _ROWS_POOL_R)
+    return row_topk(block_scores(qc, kc, q.shape[2] // 64), topk)
+
+
 def attn_fwd(q, k, v, ptr, idx, cnt):
     """(O, lse) of the list attention; q, k, v [B, H, L, D], lists over L / 64 blocks."""
     B, H, L, D = q.shape
@@ -425,7 +460,12 @@ class _Function(torch.autograd.Function):
         qr, kr, qc, kc, vc = pool_fwd(q, k, v, blk_cnt, R)
         c_cnt, c_ptr, c_idx = _coarse_meta(B, H, nb, qc.shape[2], q.device)
         oc, lse_c = attn_fwd(qc, kc, vc, c_ptr, c_idx, c_cnt)
-        sel = sel_in if sel_in is not None else _route(qr, kr, blk_cnt, R, budget, row_norm)
+        if sel_in is not None:
+            sel = sel_in
+        elif row_norm < 0:                               # original VSA: per-row top-K of the whole-block scores
+            sel = row_topk(block_scores(qc, kc, nb), budget)
+        else:
+            sel = _route(qr, kr, blk_cnt, R, budget, row_norm)
         of, lse_f = _fine_fwd(q, k, v, sel, blk_cnt, split)
         o = torch.empty_like(q)
         N.check(N.load().es_vsa_fuse_fwd(N.ptr(of), N.ptr(oc), N.ptr(gate), N.ptr(o), N.ptr(blk_cnt), B * H, L, D,
@@ -483,6 +523,34 @@ def vsa2_attention(q, k, v, gate, blk_cnt, *, R=16, topk=None, budget=None, row_
         _gate_mode(gate, q)
     b = budget_from_topk(nb, topk, budget) if selection is None else 0
     o, qp, qi, kp, ki = _Function.apply(q, k, v, gate, blk_cnt, int(R), b, ROW_NORMS[row_norm], GATE_ACTS[gate_act],
+                                        selection, _check_split(split_kv))
+    if return_selection:
+        return o, Selection(qp, qi, kp, ki)
+    return o
+
+
+def vsa_attention(q, k, v, blk_cnt, topk, *, weight=None, backend="auto", selection: Optional[Selection] = None,
+                  return_selection=False, split_kv=None):
+    """Original VSA attention (64-token blocks): O = O_fine + W * repeat(O_coarse) (reference: echosparse/vsa/ops.py:574-601).
+
+    Router: whole-block means q_c, k_c; S = (q_c @ k_c^T) / sqrt(D) rounded as the original's bf16 / fp16 Torch ops; every
+    query block keeps exactly min(topk, NB) kv blocks (score descending, ties to the smaller kv index). `weight` is a full
+    [B, H, L, D] direct weight, no activation; None means W = 1. Coarse attention, fine attention, fusion and the backward
+    are the kernels shared with VSA2; padded slots are never pooled, output 0 and get zero gradient."""
+    if backend not in ("auto", "generic"):
+        raise ValueError(f"unknown backend {backend!r}: this build has the one sm_100a backend ('auto' or 'generic')")
+    _check_tokens(q, k, v)
+    if weight is not None and weight.shape != q.shape:
+        raise ValueError(f"weight must be [B, H, L, D] like q, got {tuple(weight.shape)}")
+    nb = q.shape[2] // 64
+    blk_cnt = blk_cnt.to(torch.int32).contiguous()
+    if blk_cnt.numel() != nb:
+        raise RuntimeError("blk_cnt must have one entry per 64-token block")
+    if weight is not None:
+        weight = weight.contiguous()
+        if weight.dtype != q.dtype:
+            raise RuntimeError("weight must have the dtype of q")
+    o, qp, qi, kp, ki = _Function.apply(q, k, v, weight, blk_cnt, _ROWS_POOL_R, int(topk), -1, GATE_ACTS["identity"],
                                         selection, _check_split(split_kv))
     if return_selection:
         return o, Selection(qp, qi, kp, ki)

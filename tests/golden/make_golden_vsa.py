@@ -64,6 +64,19 @@ def main(root):
     o, lse = rep.rep_fine_reference(q, k, v, cnt, rep.pack_bits(a), rep.pack_bits(ab), mid_reps=4)
     out.update(tiers_o=h16(o), tiers_lse=f32(lse))
 
+    # E: original VSA: block scores (token dtype, stored as float32), per-row top-3, full operator with a direct weight
+    q, k, v, gate, cnt, dout = vsa_case("route")
+    S = ref.vsa_block_scores(q, k, cnt)
+    out["rows_scores"] = f32(S)
+    out["rows_mask"] = ref.row_topk_mask(S, 3).numpy()
+    q, k, v, gate, cnt, dout = vsa_case("full")
+    mask = vsa_mask("full", cnt.numel())
+    w = torch.tanh(gate.float())[..., None].expand(-1, -1, -1, q.shape[-1]).to(q.dtype).contiguous()
+    leaves = [x.double().clone().requires_grad_(True) for x in (q, k, v, w)]
+    o, _ = ref.vsa_reference(*leaves, cnt, mask, dtype=q.dtype)
+    g = torch.autograd.grad(o, leaves, dout.double())
+    out.update(vsa_o=h16(o), vsa_dq=h16(g[0]), vsa_dk=h16(g[1]), vsa_dv=h16(g[2]), vsa_dw=h16(g[3]))
+
     np.savez_compressed(os.path.join(HERE, "vsa2.npz"), **out)
     print({n: (a.shape, str(a.dtype)) for n, a in out.items()})
 
