@@ -91,6 +91,12 @@ def inject_fallback(q, rate, scale, seed):
     return len(pick)
 
 
+def sink_of(workload):
+    """First kv block of the text tokens (always computed), or None: hunyuan_video.py:66 of the reference."""
+    grid, _, _, _, text = synthetic.WORKLOADS[workload]
+    return synthetic.grid_tokens(grid) // 64 if text else None
+
+
 def build_job(args, rank, world, device):
     """Inputs of this rank's head shard, and an attention processor taken through the dense and the full step on the
     previous step's (perturbed) inputs, so that the next call is a sparse step."""
@@ -102,8 +108,8 @@ def build_job(args, rank, world, device):
                                threshold=args.threshold, min_blocks=1)
     for b in range(branches):
         qp, kp, vp = synthetic.branch_qkv(grid, cid, b, heads, device, text, prev=True)
-        attn(qp, kp, vp, 0, b, layer=1)          # dense: log2 LSE of the perturbed inputs -> offset
-        attn(qp, kp, vp, 1, b, layer=1)          # full step: first mass map, exact LSE of the perturbed inputs
+        attn(qp, kp, vp, 0, b, layer=1, sink=sink_of(args.workload))    # dense: log2 LSE of the perturbed inputs -> offset
+        attn(qp, kp, vp, 1, b, layer=1, sink=sink_of(args.workload))    # full step: first mass map, exact LSE
         del qp, kp, vp
     # Two versions of every branch's Q that differ on a seeded 0.5 % of the (tile, head) pairs (Q scaled by 3 there).
     # Steps alternate between them, so every step meets that share of tiles with an offset that is far off (in one
@@ -117,17 +123,17 @@ def build_job(args, rank, world, device):
     return attn, inputs, heads, injected
 
 
-def run_steps(attn, inputs, first_step, n):
+def run_steps(attn, inputs, first_step, n, sink=None):
     outs = None
     for i in range(n):
-        outs = [attn(q[(first_step + i) & 1], k, v, first_step + i, b, layer=1) for b, (q, k, v) in enumerate(inputs)]
+        outs = [attn(q[(first_step + i) & 1], k, v, first_step + i, b, layer=1, sink=sink)
+                for b, (q, k, v) in enumerate(inputs)]
     return outs
 
 
-def layer_flops(attn, inputs):
-    """Algorithmic FLOP of one step on this rank: every branch uses branch 0's selection."""
+def layer_flops(attn, inputs, L):
+    """Algorithmic FLOP of one step on this rank (L tokens, this rank's heads): every branch uses branch 0's selection."""
     st = attn._states[(0, 1)]
-    L = inputs[0][1].shape[1]
     return len(inputs) * synthetic.step_flops(L, st.counts, st.blocks, st.refine, st.skip_bits)
 
 
@@ -179,6 +185,9 @@ def main():
     ap.add_argument("--threshold", type=float, default=60.0, help="flag threshold on |log2 row sum| (reference: 60)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ulysses", action="store_true",
+                    help="N > 1 only: the caller is sequence-sharded; q, k, v and the output cross the ranks by all-to-all "
+                         "(NCCL) inside the timed region, the attention itself stays head-sharded")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -211,8 +220,20 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    sink = sink_of(args.workload)
+    if args.ulysses and dist is not None:
+        # the caller's layout: this rank's tokens of every head. The exchange back to heads is part of every step.
+        from self_trainable_or_free_attn_b200 import ulysses
+        if L % world or heads_all % world:
+            raise SystemExit(f"--ulysses needs tokens ({L}) and heads ({heads_all}) divisible by the ranks ({world})")
+        inputs = [(tuple(ulysses.heads_to_seq(t) for t in q), ulysses.heads_to_seq(k), ulysses.heads_to_seq(v))
+                  for q, k, v in inputs]
+        attn_call = ulysses.UlyssesAttention(attn)
+    else:
+        attn_call = attn
+
     # ---- warm-up, then the device-resident timed region
-    run_steps(attn, inputs, 2, args.warmup)
+    run_steps(attn_call, inputs, 2, args.warmup, sink)
     names = ["sparse_attention", "block_attention", "exact_fallback", "compensate_fallback", "block_means", "select_blocks",
              "estimate_skipped", "full_step_scales", "reps_build"]
     timer = K.KernelTimer(names)
@@ -224,7 +245,7 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
-    run_steps(attn, inputs, 2 + args.warmup, args.steps)
+    run_steps(attn_call, inputs, 2 + args.warmup, args.steps, sink)
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
@@ -233,7 +254,7 @@ def main():
     K.set_kernel_timer(None)
     kernel_ms = timer.ms("sparse_attention")
     status = _native.device_status()
-    flops_rank = layer_flops(attn, inputs)
+    flops_rank = layer_flops(attn, inputs, L)
     flagged = int(attn._states[(0, 1)].flags.sum())          # branch 0, last timed step
 
     # ---- end to end: host buffers, H2D of q, k, v and D2H of the output inside the timed region, double-buffered
@@ -257,7 +278,7 @@ def main():
                     d.copy_(s, non_blocking=True)
                 ready[j].record(copy_stream)
             main_stream.wait_event(ready[j])
-            out = attn(*dev_in[slot], step, b, layer=1)
+            out = attn_call(*dev_in[slot], step, b, layer=1, sink=sink)
             freed[j].record(main_stream)
             done = torch.cuda.Event()
             done.record(main_stream)
@@ -311,7 +332,9 @@ def main():
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "tokens": L, "heads": heads_all, "branches": branches, "density": density,
-                   "partition": f"heads over {world} GPU(s), both CFG branches of a head together",
+                   "partition": (f"heads over {world} GPU(s), both CFG branches of a head together"
+                                 + ("; sequence-sharded caller: q, k, v and the output cross the ranks by NCCL all-to-all every "
+                                    "step (Ulysses)" if args.ulysses and world > 1 else "")),
                    "step": "select + block means + representatives + fused sparse attention + fallback + estimates, "
                            "both branches", "algorithmic_tflop_per_step": flops_all / 1e12,
                    "l2": "inputs (q, k, v of a branch >> 126 MB) exceed L2 between iterations",

@@ -86,6 +86,54 @@ class _LayerState:
         return self.keeps[self.kc]
 
 
+class _CompactState:
+    """Compact state of one layer (reference: attention.py:72-97): the offsets of every branch and the plans, each a pair
+    of bit masks (exact blocks, blocks skipped by the block-mean compensation), 2 x H x nq x words x 4 bytes: 12 MB per
+    plan at 75,600 tokens and 40 heads against the 310 MB of a `_LayerState`. Branch 0 writes the other of two plans for
+    the next step while later branches still read the current one."""
+
+    def __init__(self, L, H, device):
+        nb = cdiv(L, BK)
+        self.L, self.H, self.device = L, H, device
+        self.words = max(next_power_of_2(nb) // 32, 4 * cdiv(nb, 128))
+        self.plans = []
+        self.offsets = {}
+        self.ready = set()          # branches that have run the full step
+        self.current = None         # (plan, step) used by the branches of this step
+        self.pending = None         # (plan, step) made by branch 0 for the next step
+
+    def plan(self, i):
+        while len(self.plans) <= i:
+            shape = (self.H, cdiv(self.L, BM), self.words)
+            self.plans.append(tuple(torch.full(shape, -1, device=self.device, dtype=torch.int32) for _ in range(2)))
+        return self.plans[i]
+
+    def offset(self, branch):
+        if branch not in self.offsets:
+            self.offsets[branch] = torch.full((cdiv(self.L, BM) * BM, self.H), 1e30, device=self.device)
+        return self.offsets[branch]
+
+
+class _PlanScratch:
+    """Per-call tensors of the compact path, shared by all layers (reference: attention.py:99-117)."""
+
+    def __init__(self, L, H, device, refine_width):
+        nq, nb = cdiv(L, BM), cdiv(L, BK)
+        self.shape = (L, H, refine_width)
+        self.mass = torch.empty(H, nq, nb, device=device)
+        self.keep = torch.empty(H, nq, nb, device=device, dtype=torch.uint8)
+        self.next_keep = torch.empty(H, nq, nb, device=device, dtype=torch.uint8)
+        self.scale_exact = torch.empty(H, nq, device=device)
+        self.scale_skip = torch.empty(H, nq, device=device)
+        self.counts = torch.empty(nq, H, device=device, dtype=torch.int32)
+        self.blocks = torch.zeros(nq, H, nb, device=device, dtype=torch.int32)
+        self.refine = torch.empty(nq, H, refine_width, device=device, dtype=torch.int32)
+        self.refine_counts = torch.empty(nq, H, device=device, dtype=torch.int32)
+        self.means = torch.empty(nq, H, nb, device=device, dtype=torch.int32)
+        self.mean_counts = torch.empty(nq, H, device=device, dtype=torch.int32)
+        self.next_offset = torch.empty(nq * BM, H, device=device)
+
+
 class _Buffers:
     """Per-call scratch for one sequence shape (reference: attention.py:119-130)."""
 
@@ -109,10 +157,15 @@ class EchoSparseAttention:
     other conditioning tokens placed after the video tokens). `rows` is accepted for signature compatibility.
 
     `gpu`: "auto" or "b200". `min_blocks`: sequences with fewer kv blocks run dense (the reference's constant 64).
+    `state`: "layer" keeps the reference's B200 state per (branch, layer) (mass map, keep masks, lists); "compact" keeps
+    only the offsets and the bit-mask plans per layer (the reference's state on its other GPUs, attention.py:272-330) and
+    rebuilds the lists from the plan every step: 25 x less resident state for two more small kernels per call.
     """
 
     def __init__(self, density=0.10, dense_steps=10, dense_layers=(0,), refine_iters=6, threshold=60.0, gpu="auto",
-                 min_blocks=MIN_BLOCKS):
+                 min_blocks=MIN_BLOCKS, state="layer"):
+        assert state in ("layer", "compact"), "state must be 'layer' or 'compact'"
+        self.state = state
         assert dense_steps >= 2, "the first sparse step needs the LSE of a dense step and a full-block step"
         self.density = density
         self.dense_steps = dense_steps
@@ -131,7 +184,11 @@ class EchoSparseAttention:
 
     def reset(self):
         for st in self._states.values():
-            st.ready = False
+            if isinstance(st, _CompactState):
+                st.ready.clear()
+                st.current = st.pending = None
+            else:
+                st.ready = False
 
     def __call__(self, q, k, v, step, branch, layer, sink=None, rows=None):
         B, L, H, D = q.shape
@@ -144,7 +201,71 @@ class EchoSparseAttention:
             self._device = q.device
         if layer in self.dense_layers or cdiv(L, BK) < self.min_blocks:
             return dense_attention(q, k, v, K=self.K)
+        if self.state == "compact":
+            return self._call_compact(q, k, v, step, branch, layer, sink)
         return self._call_b200(q, k, v, step, branch, layer, sink)
+
+    def _call_compact(self, q, k, v, step, branch, layer, sink):
+        """The schedule of `_call_b200` on the compact state (reference: attention.py:272-330): a step reads its plan,
+        rebuilds the lists, runs the fused kernels and, in branch 0, selects and packs the plan of the next step."""
+        L, H, D = q[0].shape
+        st = self._states.get(layer)
+        if st is None or st.L != L:
+            self._states[layer] = None
+            st = self._states[layer] = _CompactState(L, H, q.device)
+        offset = st.offset(branch)
+        if branch == 0 and step >= self.dense_steps:
+            st.current = st.pending if st.pending is not None and st.pending[1] == step else None
+            st.pending = None
+        full = step == self.dense_steps - 1
+        sparse = step >= self.dense_steps and branch in st.ready and st.current is not None and st.current[1] == step
+        if not (full or sparse):
+            out, lse = dense_attention(q, k, v, return_lse=True, K=self.K)
+            offset[:L].copy_(lse[0].t() * LOG2E)
+            return out
+        K = self.K
+        q, k, v = q[0].contiguous(), k[0].contiguous(), v[0].contiguous()
+        top, refined = self._budget(cdiv(L, BK))
+        width = -(-refined // 32) * 32
+        buf = self._scratch(L, H, D, q.device)
+        ps = self._plan_scratch
+        if ps is None or ps.shape != (L, H, width):
+            self._plan_scratch = None
+            ps = self._plan_scratch = _PlanScratch(L, H, q.device, width)
+        out = torch.empty_like(q)
+        if full:
+            ps.keep.fill_(1)
+            ps.mass.zero_()
+            K.block_attention(q, k, v, out, buf.all_counts, buf.all_blocks, offset, ps.next_offset, buf.flags,
+                              mass=ps.mass, threshold=self.threshold)
+            K.exact_fallback(q, k, v, out, buf.all_counts, buf.all_blocks, ps.next_offset, buf.flags)
+            K.full_step_scales(offset, ps.next_offset, ps.scale_exact, ps.scale_skip, L)
+            st.ready.add(branch)
+        else:
+            exact, skip = st.plan(st.current[0])
+            K.rebuild_plan(exact, skip, ps.keep, ps.counts, ps.blocks, ps.refine, ps.refine_counts, ps.means,
+                           ps.mean_counts)
+            K.block_means(k, v, buf.k_mean, buf.v_mean)
+            buf.reps.build(q, k, v)
+            if branch == 0:
+                ps.mass.zero_()
+            K.sparse_attention(q, k, v, buf.k_mean, buf.v_mean, skip, out, ps.counts, ps.blocks, offset, ps.next_offset,
+                               buf.flags, ps.refine, buf.reps.k, buf.reps.v, buf.reps.log_counts,
+                               mass=ps.mass if branch == 0 else None, threshold=self.threshold)
+            K.exact_fallback(q, k, v, out, ps.counts, ps.blocks, ps.next_offset, buf.flags)
+            K.compensate_fallback(q, buf.k_mean, buf.v_mean, ps.keep, ps.next_offset, out, buf.flags)
+            if branch == 0:
+                K.estimate_skipped(q, buf.k_mean, ps.keep, offset, ps.next_offset, ps.mass, ps.scale_exact, ps.scale_skip)
+        if branch == 0:
+            # the next step's plan, after this step's last use of the current one in a single branch
+            plan = 0 if st.current is None else st.current[0] ^ (len(st.offsets) > 1)
+            exact, skip = st.plan(plan)
+            K.select_blocks(ps.mass, ps.keep, ps.scale_exact, ps.scale_skip, ps.next_keep, ps.counts, ps.blocks, buf.flags,
+                            skip, ps.refine, top, refined, L, sink=1 << 30 if sink is None else sink)
+            K.pack_plan(ps.next_keep, exact)
+            st.pending = (plan, step + 1)
+        offset.copy_(ps.next_offset)
+        return out[None]
 
     def _call_b200(self, q, k, v, step, branch, layer, sink):
         L, H, D = q[0].shape

@@ -68,3 +68,44 @@ def test_branches_of_a_head_share_structure_but_not_noise():
     assert not torch.equal(a[0], b[0])
     prev = synthetic.head_qkv(GRID, 2, 0, 3, "cpu", prev=True, dtype=torch.float32)
     assert 0 < (prev[0] - a[0]).abs().max() < 0.2 and torch.equal(prev[2], a[2])
+
+
+# ---------------------------------------------------------------------------------------------- Ulysses exchange
+def _ulysses_worker(rank, world, port, out_dir):
+    from self_trainable_or_free_attn_b200 import ulysses
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    L, H, D = 24, 4, 8
+    g = torch.Generator().manual_seed(3)
+    full = [torch.randn(1, L, H, D, generator=g) for _ in range(3)]                  # the same on every rank
+    mine = [t[:, rank * L // world:(rank + 1) * L // world].contiguous() for t in full]
+    heads = slice(rank * H // world, (rank + 1) * H // world)
+    qh = ulysses.seq_to_heads(mine[0])
+    ok_fwd = torch.equal(qh, full[0][:, :, heads])
+    ok_back = torch.equal(ulysses.heads_to_seq(qh), mine[0])
+
+    def attn(q, k, v, scale=2.0):                                                     # any per-head attention
+        p = torch.softmax(torch.einsum("blhd,bmhd->bhlm", q, k) / scale, -1)
+        return torch.einsum("bhlm,bmhd->blhd", p, v)
+
+    out = ulysses.UlyssesAttention(attn)(*mine, scale=3.0)
+    ref = attn(*full, scale=3.0)[:, rank * L // world:(rank + 1) * L // world]
+    bad = None
+    try:
+        ulysses.seq_to_heads(torch.zeros(1, 4, 3, 8))
+    except ValueError as e:
+        bad = str(e)
+    torch.save({"ok_fwd": ok_fwd, "ok_back": ok_back, "err": (out - ref).abs().max().item(), "bad": bad},
+               os.path.join(out_dir, f"u{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_ulysses_exchange_round_trip_and_attention_equivalence(tmp_path):
+    world = 2
+    mp.spawn(_ulysses_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        res = torch.load(tmp_path / f"u{r}.pt")
+        assert res["ok_fwd"] and res["ok_back"], "exchange is not the head / sequence transposition"
+        assert res["err"] < 1e-6, "sequence-sharded attention differs from the unsharded one"
+        assert "cannot be divided" in res["bad"]

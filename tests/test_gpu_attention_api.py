@@ -147,3 +147,28 @@ def test_short_sequences_run_dense_and_reset_forgets():
     assert not attn._states[(0, 1)].ready
     out = attn(*inputs[2], 2, 0, layer=1)                   # not ready: dense again
     assert rel_err(out, dense(*inputs[2])) < 1e-2
+
+
+def test_compact_plan_state_matches_the_layer_state():
+    """The compact state (offsets + bit-mask plans per layer, lists rebuilt every step; reference attention.py:272-330)
+    goes through the same kernels with the same selections as the per-(branch, layer) state: identical outputs over
+    several steps and both CFG branches, with 25 x less resident state."""
+    inputs = steps(6, seed=4)
+    a, b = make(density=0.2), make(density=0.2, state="compact")
+    outs_a, outs_b = run(a, inputs, branches=2), run(b, inputs, branches=2)
+    for i, (x, y) in enumerate(zip(outs_a, outs_b)):
+        assert torch.equal(x, y), f"call {i}: compact state differs"
+    st = b._states[1]
+    assert sorted(st.offsets) == [0, 1] and len(st.plans) == 2 and st.pending == (1 - st.current[0], 6)
+    resident = sum(t.numel() * t.element_size() for p in st.plans for t in p) + sum(t.numel() * 4 for t in st.offsets.values())
+    la = a._states[(0, 1)]
+    layer = 2 * sum(t.numel() * t.element_size() for t in (la.mass, *la.keeps, la.blocks, *la.offsets, la.skip_bits))
+    assert resident * 5 < layer
+    # a sink block and a reset
+    c = make(density=0.2, state="compact")
+    d = make(density=0.2)
+    for step, (q, k, v) in enumerate(inputs[:4]):
+        assert torch.equal(c(q, k, v, step, 0, layer=1, sink=60), d(q, k, v, step, 0, layer=1, sink=60))
+    c.reset()
+    q, k, v = inputs[0]
+    assert rel_err(c(q, k, v, 5, 0, layer=1), dense(q, k, v)) < 1e-2          # not ready: dense
