@@ -261,7 +261,8 @@ def main():
     host_in = [[[t.cpu().pin_memory() for t in q], k.cpu().pin_memory(), v.cpu().pin_memory()] for q, k, v in inputs]
     host_out = [torch.empty(k.shape, dtype=torch.bfloat16).pin_memory() for _, k, _ in inputs]
     dev_in = [[torch.empty_like(inputs[0][1]) for _ in range(3)] for _ in range(2)]
-    copy_stream = torch.cuda.Stream()
+    copy_stream = torch.cuda.Stream()           # host -> device
+    back_stream = torch.cuda.Stream()           # device -> host: its own stream, PCIe carries both directions at once
     main_stream = torch.cuda.current_stream()
 
     def e2e_steps(first_step, n):
@@ -282,11 +283,12 @@ def main():
             freed[j].record(main_stream)
             done = torch.cuda.Event()
             done.record(main_stream)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(done)
+            with torch.cuda.stream(back_stream):
+                back_stream.wait_event(done)
                 host_out[b].copy_(out, non_blocking=True)
-                out.record_stream(copy_stream)
+                out.record_stream(back_stream)
         main_stream.wait_stream(copy_stream)
+        main_stream.wait_stream(back_stream)
 
     e2e_steps(2 + args.warmup + args.steps, 1)
     barrier()

@@ -2,6 +2,7 @@
 // blocks (the block-mean compensation of fallback tiles is a mode of the attention kernel). Vectorised 16-byte loads, warp shuffles, mma.sync for the
 // one small contraction (16 sampled query rows x block-mean keys).
 #include "es_api_internal.h"
+#include "es_vsa_mma.cuh"
 
 #include <cuda_bf16.h>
 #include <math.h>
@@ -81,29 +82,28 @@ full_scale_kernel(const float* __restrict__ m, float* __restrict__ lse, float* _
 //   est[t, b] = mean over 16 sampled rows r = 128 t + 8 s of 2^min(c q_r.kmean_b - m_r + log2 len_b, 100), written into
 //   the map for blocks that were not kept; f = mean_rows 2^clamp(m - m_new); scale_exact = f / rows;
 //   scale_skip = f * clamp((sum_kept mass / rows) / sum_kept est, 1, 64).
-// One CTA (8 warps) per (tile, head); a warp takes 8 blocks at a time: S(16 x 8) by 8 mma.sync m16n8k16 over d.
-__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
+// One CTA per (8 consecutive tiles, head), one warp per tile. The block-mean keys travel through shared memory in tiles of
+// 64 blocks (cp.async, two stages, 16-byte chunks XOR-swizzled by the row) that all eight warps consume with ldmatrix:
+// S(16 sampled rows x 64 blocks) by mma.sync m16n8k16 over d. Reading the keys once per eight tiles with 16-byte accesses,
+// instead of once per tile with 4-byte ones, is what the kernel's time depends on (the keys of a head are 300 KB).
+constexpr int EST_TILES = 8;
 __global__ void __launch_bounds__(256)
 estimate_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ km,
                 const uint8_t* __restrict__ keep, const float* __restrict__ m, const float* __restrict__ mnew,
                 float* __restrict__ map, float* __restrict__ scale_exact, float* __restrict__ scale_skip,
                 float scale_log2, int L, int nb, float lb_last, int H, int nq) {
-    __shared__ float red[8][2];
-    __shared__ float fpart[8];
-    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    using namespace es::vsa;
+    __shared__ __align__(128) uint8_t tiles[2][64 * HD * 2];
+    const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int t = blockIdx.x * EST_TILES + warp;
+    const bool tv = t < nq;                                   // warps past the last tile still help with the copies
     const int g = lane >> 2, tg = lane & 3;
     // A fragments of the 16 sampled rows (row s -> query row 128 t + 8 s), all 8 k-steps
     uint32_t afr[8][4];
     const int r0 = t * 128 + 8 * g, r1 = t * 128 + 8 * (g + 8);
-    const bool v0 = r0 < L, v1 = r1 < L;
-    const __nv_bfloat16* q0 = q + ((size_t)r0 * H + h) * HD;
-    const __nv_bfloat16* q1 = q + ((size_t)r1 * H + h) * HD;
+    const bool v0 = tv && r0 < L, v1 = tv && r1 < L;
+    const __nv_bfloat16* q0 = q + ((size_t)(v0 ? r0 : 0) * H + h) * HD;
+    const __nv_bfloat16* q1 = q + ((size_t)(v1 ? r1 : 0) * H + h) * HD;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
         const int d = ks * 16 + tg * 2;
@@ -114,78 +114,99 @@ estimate_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
     }
     const float m0 = v0 ? m[(size_t)r0 * H + h] : 0.f, m1 = v1 ? m[(size_t)r1 * H + h] : 0.f;
     int nsv = 0;
-    for (int s = 0; s < 16; ++s) nsv += (t * 128 + 8 * s) < L;
+    for (int s = 0; s < 16; ++s) nsv += tv && (t * 128 + 8 * s) < L;
     const float inv_ns = 1.0f / fmaxf((float)nsv, 1.0f);
-    const size_t mbase = ((size_t)h * nq + t) * nb;
+    const size_t mbase = ((size_t)h * nq + (tv ? t : 0)) * nb;
+    const int nct = (nb + 63) / 64;
+    auto load_keys = [&](int stage, int ct) {
+        const uint32_t dst = smem_addr(tiles[stage]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {                         // 64 rows x 16 chunks of 16 bytes over 256 threads
+            const int idx = i * 256 + tid, row = idx >> 4, ch = idx & 15;
+            const int blk = min(ct * 64 + row, nb - 1);       // rows past the last block repeat it; their columns are masked
+            cp16(dst + tile_off<HD>(row, ch), km + ((size_t)blk * H + h) * HD + ch * 8);
+        }
+    };
+    load_keys(0, 0);
+    cp_commit();
     float num = 0.f, den = 0.f;
-    for (int c0 = warp * 8; c0 < nb; c0 += 64) {
-        const int col = c0 + g;                       // B fragment: column n = lane / 4
-        const bool cv = col < nb;
-        const __nv_bfloat16* kr = km + ((size_t)(cv ? col : 0) * H + h) * HD;
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int ct = 0; ct < nct; ++ct) {
+        if (ct + 1 < nct) load_keys((ct + 1) & 1, ct + 1);
+        cp_commit();
+        cp_wait<1>();
+        __syncthreads();
+        const uint32_t tile = smem_addr(tiles[ct & 1]);
+        float acc[8][4];
 #pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            const int d = ks * 16 + tg * 2;
-            const uint32_t b0 = cv ? *reinterpret_cast<const uint32_t*>(kr + d) : 0u;
-            const uint32_t b1 = cv ? *reinterpret_cast<const uint32_t*>(kr + d + 8) : 0u;
-            mma_bf16_16816(acc, afr[ks], b0, b1);
-        }
-        // acc[0], acc[1]: row g, columns c0 + 2 tg, + 1; acc[2], acc[3]: row g + 8
-        float e[2];
+        for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 #pragma unroll
-        for (int x = 0; x < 2; ++x) {
-            const int cc = c0 + 2 * tg + x;
-            const float lb = (cc == nb - 1) ? lb_last : 6.0f;
-            const float e0 = v0 ? exp2f(fminf(acc[x] * scale_log2 - m0 + lb, 100.f)) : 0.f;
-            const float e1 = v1 ? exp2f(fminf(acc[2 + x] * scale_log2 - m1 + lb, 100.f)) : 0.f;
-            float s = e0 + e1;
-            s += __shfl_xor_sync(0xffffffffu, s, 4);
-            s += __shfl_xor_sync(0xffffffffu, s, 8);
-            s += __shfl_xor_sync(0xffffffffu, s, 16);
-            e[x] = s * inv_ns;
-        }
-        if (g == 0) {
+        for (int ks = 0; ks < 8; ++ks)
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                uint32_t b[4];
+                load_b_nk<HD>(tile, np, ks, lane, b);
+                Elt<__nv_bfloat16>::mma(acc[2 * np], afr[ks], b[0], b[1]);
+                Elt<__nv_bfloat16>::mma(acc[2 * np + 1], afr[ks], b[2], b[3]);
+            }
+        // acc[i][0], acc[i][1]: row g, blocks 64 ct + 8 i + 2 tg, + 1; acc[i][2], acc[i][3]: row g + 8
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float e[2];
 #pragma unroll
             for (int x = 0; x < 2; ++x) {
-                const int cc = c0 + 2 * tg + x;
-                if (cc < nb) {
-                    if (keep[mbase + cc] != 0) {
-                        num += map[mbase + cc];
-                        den += e[x];
-                    } else {
-                        map[mbase + cc] = e[x];
+                const int cc = ct * 64 + i * 8 + 2 * tg + x;
+                const float lb = (cc == nb - 1) ? lb_last : 6.0f;
+                const float e0 = v0 ? exp2f(fminf(acc[i][x] * scale_log2 - m0 + lb, 100.f)) : 0.f;
+                const float e1 = v1 ? exp2f(fminf(acc[i][2 + x] * scale_log2 - m1 + lb, 100.f)) : 0.f;
+                float s2 = e0 + e1;
+                s2 += __shfl_xor_sync(0xffffffffu, s2, 4);
+                s2 += __shfl_xor_sync(0xffffffffu, s2, 8);
+                s2 += __shfl_xor_sync(0xffffffffu, s2, 16);
+                e[x] = s2 * inv_ns;
+            }
+            if (g == 0 && tv) {
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    const int cc = ct * 64 + i * 8 + 2 * tg + x;
+                    if (cc < nb) {
+                        if (keep[mbase + cc] != 0) {
+                            num += map[mbase + cc];
+                            den += e[x];
+                        } else {
+                            map[mbase + cc] = e[x];
+                        }
                     }
                 }
             }
         }
+        __syncthreads();
     }
+    cp_wait<0>();
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         num += __shfl_xor_sync(0xffffffffu, num, o);
         den += __shfl_xor_sync(0xffffffffu, den, o);
     }
-    // f over the tile's rows: threads 0..127
+    if (!tv) return;
+    // f over the tile's rows: four per lane, summed in a fixed order
     float f = 0.f;
-    if (tid < 128) {
-        const int row = t * 128 + tid;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int row = t * 128 + 32 * i + lane;
         if (row < L) {
             const float a = m[(size_t)row * H + h], b = mnew[(size_t)row * H + h];
-            f = exp2f(fminf(fmaxf(a - b, -100.f), 100.f));
+            f += exp2f(fminf(fmaxf(a - b, -100.f), 100.f));
         }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) f += __shfl_xor_sync(0xffffffffu, f, o);
-    if (lane == 0) { red[warp][0] = num; red[warp][1] = den; fpart[warp] = f; }
-    __syncthreads();
-    if (tid == 0) {
+    if (lane == 0) {
         const float nrows = (float)min(L - t * 128, 128);
-        float nn = 0.f, dd = 0.f;
-        for (int w = 0; w < 8; ++w) { nn += red[w][0]; dd += red[w][1]; }
-        const float ff = ((fpart[0] + fpart[1]) + (fpart[2] + fpart[3])) / nrows;
+        const float ff = f / nrows;
         scale_exact[h * nq + t] = ff / nrows;
         // The block-mean estimate underestimates block mass (Jensen): calibrate it on the blocks computed exactly.
-        nn /= nrows;
-        const float c = dd > 0.f ? fminf(fmaxf(nn / fmaxf(dd, 1e-30f), 1.0f), 64.0f) : 1.0f;
+        const float nn = num / nrows;
+        const float c = den > 0.f ? fminf(fmaxf(nn / fmaxf(den, 1e-30f), 1.0f), 64.0f) : 1.0f;
         scale_skip[h * nq + t] = ff * c;
     }
 }
@@ -224,7 +245,7 @@ extern "C" int es_estimate_skipped(const void* q, const void* k_mean, const uint
     if (L <= 0 || H <= 0) return set_error(-1, "es_estimate_skipped: L and H must be positive");
     const int nq = (L + 127) / 128, nb = (L + 63) / 64;
     const int tail = L - (nb - 1) * 64;
-    estimate_kernel<<<dim3(nq, H), 256, 0, (cudaStream_t)stream>>>(
+    estimate_kernel<<<dim3((nq + EST_TILES - 1) / EST_TILES, H), 256, 0, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_mean, keep, offset, lse, mass, scale_exact, scale_skip,
         LOG2E_F / sqrtf((float)HD), L, nb, log2f((float)tail), H, nq);
     ES_CHECK_LAUNCH("estimate_skipped");
