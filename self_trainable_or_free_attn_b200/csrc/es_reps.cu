@@ -201,7 +201,8 @@ constexpr int XS = 132;           // float row stride of X and of the centroids
 constexpr int PS = 65;            // float row stride of the probe scores
 constexpr int MS = 136;           // bf16 row stride of the metric in shared memory
 constexpr int KM_BLOCKS = 4;      // kv blocks per CTA: the metric is loaded into shared memory once for all of them
-constexpr int KM_SMEM = 128 * MS * 2 + 64 * KS * 2 + 64 * XS * 4 + 64 * PS * 4 + 4 * XS * 4 + 4 * 64 * 4 + 64 * 4 + 64 * 4;
+constexpr int KM_SMEM = 128 * MS * 2 + 64 * KS * 2 + 64 * XS * 4 + 64 * PS * 4 + 4 * XS * 4 + 4 * 64 * 4 + 64 * 4 + 64 * 4 +
+                        4 * 64 * 4 * 4 + 2 * 4 * 128 * 4;      // + partial dots [4][64][4] and partial centroid sums [2][4][128]
 
 __global__ void __launch_bounds__(256, 2)
 kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
@@ -217,6 +218,9 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     float* wpart = cen + 4 * XS;                                                    // [4][64]
     float* w = wpart + 4 * 64;                                                      // [64]
     int* lab = reinterpret_cast<int*>(w + 64);                                      // [64]
+    float* dpart = reinterpret_cast<float*>(lab + 64);                              // [4 d quarters][64 tokens][4 clusters]
+    float* cpart = dpart + 4 * 64 * 4;                                              // [2 token halves][4 clusters][128]
+    __shared__ float wspart[2][4];
     __shared__ float cw[4], cnorm[4];
     __shared__ int s_changed;
     __shared__ float s_cnt[4];
@@ -360,16 +364,36 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
 
     // weighted centroids of the current labels (thread -> cluster tid / 64, dims 2 (tid % 64), +1); keep_old: an emptied
     // cluster keeps its centroid. Also the cluster weights and the squared norms of the centroids.
+    // The Lloyd iterations are bound by shared-memory bandwidth, so both phases read X as few times as the thread layout
+    // allows: here thread (token half, dim) sweeps 32 tokens for all four clusters (X read once, labels and weights as
+    // broadcasts), then thread (cluster, dim pair) combines the two halves in a fixed order.
     auto update_centroids = [&](bool keep_old) {
-        const int c = tid >> 6, d = 2 * (tid & 63);
-        float s0 = 0.f, s1 = 0.f, ws = 0.f;
-        for (int t = 0; t < nvalid; ++t) {
-            const float wt = (lab[t] == c) ? w[t] : 0.f;
-            const float2 x = *reinterpret_cast<const float2*>(sX + t * XS + d);
-            s0 = fmaf(wt, x.x, s0);
-            s1 = fmaf(wt, x.y, s1);
-            ws += wt;
+        {
+            const int d = tid & 127, th = tid >> 7;
+            float sc[4] = {0.f, 0.f, 0.f, 0.f}, wc[4] = {0.f, 0.f, 0.f, 0.f};
+            const int t1 = min(32 * th + 32, nvalid);
+            for (int t = 32 * th; t < t1; ++t) {
+                const int l = lab[t];
+                const float wt = w[t], x = sX[t * XS + d];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float wl = l == c ? wt : 0.f;
+                    sc[c] = fmaf(wl, x, sc[c]);
+                    wc[c] += wl;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) cpart[(th * 4 + c) * 128 + d] = sc[c];
+            if (d == 0) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) wspart[th][c] = wc[c];
+            }
         }
+        __syncthreads();
+        const int c = tid >> 6, d = 2 * (tid & 63);
+        const float s0 = cpart[c * 128 + d] + cpart[(4 + c) * 128 + d];
+        const float s1 = cpart[c * 128 + d + 1] + cpart[(4 + c) * 128 + d + 1];
+        const float ws = wspart[0][c] + wspart[1][c];
         float c0, c1;
         if (!keep_old || ws > 0.f) {
             const float inv = 1.0f / fmaxf(ws, 1e-6f);
@@ -390,32 +414,42 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     };
     update_centroids(false);
     for (int it = 0; it < iters; ++it) {
-        // thread -> (token tid / 4, cluster tid % 4)
-        const int t = tid >> 2, c = tid & 3;
-        float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-        const float* xr = sX + t * XS;
-        const float* cr = cen + c * XS;
-#pragma unroll 8
-        for (int d = 0; d < HD; d += 4) {
-            const float4 x = *reinterpret_cast<const float4*>(xr + d);
-            const float4 y = *reinterpret_cast<const float4*>(cr + d);
-            d0 = fmaf(x.x, y.x, d0); d1 = fmaf(x.y, y.y, d1); d2 = fmaf(x.z, y.z, d2); d3 = fmaf(x.w, y.w, d3);
-        }
-        const float dot = (d0 + d1) + (d2 + d3);
-        float dist = cw[c] > 0.f ? cnorm[c] - 2.0f * dot : INFINITY;
-        int best = c;
-        // first minimum among the four clusters of this token (lanes 4 t' .. 4 t' + 3)
+        // partial dot products: warp -> (d quarter warp % 4, token half warp / 4), lane -> token; the centroid rows are
+        // read as broadcasts, X once; then one thread per token adds the four quarters in a fixed order
+        {
+            const int dq = warp & 3, tk = 32 * (warp >> 2) + lane;
+            float dt[4] = {0.f, 0.f, 0.f, 0.f};
+            const float* xr = sX + tk * XS + 32 * dq;
 #pragma unroll
-        for (int o = 1; o < 4; o <<= 1) {
-            const float od = __shfl_xor_sync(0xffffffffu, dist, o);
-            const int ob = __shfl_xor_sync(0xffffffffu, best, o);
-            if (od < dist || (od == dist && ob < best)) { dist = od; best = ob; }
+            for (int i = 0; i < 8; ++i) {
+                const float4 x = *reinterpret_cast<const float4*>(xr + 4 * i);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float4 y = *reinterpret_cast<const float4*>(cen + c * XS + 32 * dq + 4 * i);
+                    dt[c] = fmaf(x.x, y.x, dt[c]); dt[c] = fmaf(x.y, y.y, dt[c]);
+                    dt[c] = fmaf(x.z, y.z, dt[c]); dt[c] = fmaf(x.w, y.w, dt[c]);
+                }
+            }
+            *reinterpret_cast<float4*>(dpart + (dq * 64 + tk) * 4) = make_float4(dt[0], dt[1], dt[2], dt[3]);
+        }
+        __syncthreads();
+        const int t = tid, c = 0;                     // threads 0 .. 63: one token each
+        int best = 0;
+        if (tid < 64) {
+            float bd = INFINITY;
+#pragma unroll
+            for (int cc = 0; cc < 4; ++cc) {
+                const float dot = (dpart[(0 * 64 + t) * 4 + cc] + dpart[(1 * 64 + t) * 4 + cc]) +
+                                  (dpart[(2 * 64 + t) * 4 + cc] + dpart[(3 * 64 + t) * 4 + cc]);
+                const float dist = cw[cc] > 0.f ? cnorm[cc] - 2.0f * dot : INFINITY;
+                if (dist < bd || (cc == 0)) { if (cc == 0 || dist < bd) { bd = dist; best = cc; } }
+            }
         }
         if (tid == 0) s_changed = 0;
         __syncthreads();
-        if (c == 0 && t < nvalid && best != lab[t]) atomicAdd(&s_changed, 1);
+        if (tid < 64 && c == 0 && t < nvalid && best != lab[t]) atomicAdd(&s_changed, 1);
         __syncthreads();
-        if (c == 0) lab[t] = best;
+        if (tid < 64) lab[t] = best;
         const int changed = s_changed;
         __syncthreads();
         update_centroids(true);
