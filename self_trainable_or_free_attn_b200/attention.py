@@ -38,6 +38,12 @@ def dense_attention(q, k, v, return_lse=False, K=None):
     if K is None:
         K = backends.kernels(backends.resolve("auto", q.device))
     B, L, H, D = q.shape
+    if k.shape[1] != L:
+        # cross-shaped calls (text rows against all tokens, video rows against text tokens) are outside the sparse path:
+        # the reference sends them to its library dense kernel (FlashAttention-4, backends.py:50-59); here torch's is used
+        assert not return_lse, "the LSE is only needed for self-attention"
+        o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+        return o.transpose(1, 2).contiguous()
     assert B == 1
     nq, nb = cdiv(L, BM), cdiv(L, BK)
     dev = q.device
