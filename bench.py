@@ -63,6 +63,9 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append(line)
 
+    def count(self):
+        return len(self.lines) if self.proc is not None else 1 << 30
+
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
@@ -232,16 +235,17 @@ def main():
     else:
         attn_call = attn
 
-    # ---- warm-up, then the device-resident timed region
+    # ---- warm-up, then the device-resident timed region. The clock sampler runs from the warm-up on (the same load), so
+    # that a timed region of a few tens of milliseconds (many GPUs, few steps) still has samples.
+    sampler = ClockSampler(local)
+    sampler.start()
     run_steps(attn_call, inputs, 2, args.warmup, sink)
     names = ["sparse_attention", "block_attention", "exact_fallback", "compensate_fallback", "block_means", "select_blocks",
              "estimate_skipped", "full_step_scales", "reps_build"]
     timer = K.KernelTimer(names)
-    sampler = ClockSampler(local)
     barrier()
     K.set_kernel_timer(timer)
     launches0 = _native.launch_count()
-    sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     e0.record()
@@ -249,9 +253,15 @@ def main():
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop()
     launches = _native.launch_count() - launches0
     K.set_kernel_timer(None)
+    extra = 0
+    while sampler.count() < 3 and extra < 40:          # nvidia-smi needs ~0.3 s for its first lines: keep the load on
+        run_steps(attn_call, inputs, 2 + args.warmup + args.steps + extra, 2, sink)
+        torch.cuda.synchronize()
+        extra += 2
+    clocks = sampler.stop()
+    clocks["window"] = "warm-up + timed steps" + (f" + {extra} more steps of the same load" if extra else "")
     kernel_ms = timer.ms("sparse_attention")
     status = _native.device_status()
     flops_rank = layer_flops(attn, inputs, L)

@@ -219,10 +219,8 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     float* w = wpart + 4 * 64;                                                      // [64]
     int* lab = reinterpret_cast<int*>(w + 64);                                      // [64]
     float* dpart = reinterpret_cast<float*>(lab + 64);                              // [4 d quarters][64 tokens][4 clusters]
-    float* cpart = dpart + 4 * 64 * 4;                                              // [2 token halves][4 clusters][128]
-    __shared__ float wspart[2][4];
-    __shared__ float cw[4], cnorm[4];
-    __shared__ int s_changed;
+    // dpart is followed by 4 KB more, so that the two together hold [4][4][128] partial sums
+    __shared__ float cw[4];
     __shared__ float s_cnt[4];
     const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tg = lane & 3;
@@ -245,10 +243,22 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
                          k + ((size_t)(j * 64 + (okr ? r : 0)) * H + h) * HD + c16 * 8, okr ? 16 : 0);
     }
     cp_async_commit();
+    const int mt = warp & 3, nh = warp >> 2;
+    // this thread's A fragments of the probe scores (probes 16 mt .. +15), fetched while the K tile is in flight
+    uint32_t pa[8][4];
+    {
+        const __nv_bfloat16* p0 = probes + ((size_t)h * NP + 16 * mt + g) * HD + 2 * tg;
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            pa[ks][0] = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16));
+            pa[ks][1] = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16));
+            pa[ks][2] = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 8));
+            pa[ks][3] = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16 + 8));
+        }
+    }
     cp_async_wait<0>();
     __syncthreads();
 
-    const int mt = warp & 3, nh = warp >> 2;
     // A fragments of this warp's 16 tokens (rows 16 mt ..), all 8 k-steps: shared by both contractions below? No: the
     // probe scores use K as the B operand. Only X uses these.
     {
@@ -284,19 +294,15 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
         }
     }
     {
-        // probe scores: probes 16 mt .. +15 (A, from global), tokens 32 nh .. +31 (B = K rows, from shared memory)
+        // probe scores: probes 16 mt .. +15 (A, in registers), tokens 32 nh .. +31 (B = K rows, from shared memory)
         float acc[4][4];
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
             for (int x = 0; x < 4; ++x) acc[nt][x] = 0.f;
-        const __nv_bfloat16* p0 = probes + ((size_t)h * NP + 16 * mt + g) * HD + 2 * tg;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-            const uint32_t a0 = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16));
-            const uint32_t a1 = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16));
-            const uint32_t a2 = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 8));
-            const uint32_t a3 = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16 + 8));
+            const uint32_t a0 = pa[ks][0], a1 = pa[ks][1], a2 = pa[ks][2], a3 = pa[ks][3];
 #pragma unroll
             for (int nt = 0; nt < 4; ++nt) {
                 const __nv_bfloat16* kr = sK + (32 * nh + 8 * nt + g) * KS + ks * 16 + 2 * tg;
@@ -362,54 +368,57 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     cp_async_commit();
     __syncthreads();
 
-    // weighted centroids of the current labels (thread -> cluster tid / 64, dims 2 (tid % 64), +1); keep_old: an emptied
-    // cluster keeps its centroid. Also the cluster weights and the squared norms of the centroids.
-    // The Lloyd iterations are bound by shared-memory bandwidth, so both phases read X as few times as the thread layout
-    // allows: here thread (token half, dim) sweeps 32 tokens for all four clusters (X read once, labels and weights as
-    // broadcasts), then thread (cluster, dim pair) combines the two halves in a fixed order.
+    // Weighted centroids of the current labels; keep_old: an emptied cluster keeps its centroid. Also the cluster weights
+    // and the squared norms of the centroids (two warp partials per cluster in wpart[0..7]).
+    // The Lloyd iterations are bound by instruction issue, so the sweep does one multiply-add per (token, dim): a token's
+    // label is the same for every thread, so the branch on it is uniform. Thread (token quarter, dim pair) sweeps 16
+    // tokens; thread (cluster, dim pair) then adds the four quarters in a fixed order.
+    float* qpart = dpart;                             // [4 token quarters][4 clusters][128]: dpart and cpart, both dead here
     auto update_centroids = [&](bool keep_old) {
         {
-            const int d = tid & 127, th = tid >> 7;
-            float sc[4] = {0.f, 0.f, 0.f, 0.f}, wc[4] = {0.f, 0.f, 0.f, 0.f};
-            const int t1 = min(32 * th + 32, nvalid);
-            for (int t = 32 * th; t < t1; ++t) {
+            const int dp = 2 * (tid & 63), tq = tid >> 6;
+            float2 sc[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) sc[c] = make_float2(0.f, 0.f);
+            const int t1 = min(16 * tq + 16, nvalid);
+#pragma unroll 4
+            for (int t = 16 * tq; t < t1; ++t) {
                 const int l = lab[t];
-                const float wt = w[t], x = sX[t * XS + d];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float wl = l == c ? wt : 0.f;
-                    sc[c] = fmaf(wl, x, sc[c]);
-                    wc[c] += wl;
-                }
+                const float wt = w[t];
+                const float2 x = *reinterpret_cast<const float2*>(sX + t * XS + dp);
+                if (l == 0) { sc[0].x = fmaf(wt, x.x, sc[0].x); sc[0].y = fmaf(wt, x.y, sc[0].y); }
+                else if (l == 1) { sc[1].x = fmaf(wt, x.x, sc[1].x); sc[1].y = fmaf(wt, x.y, sc[1].y); }
+                else if (l == 2) { sc[2].x = fmaf(wt, x.x, sc[2].x); sc[2].y = fmaf(wt, x.y, sc[2].y); }
+                else { sc[3].x = fmaf(wt, x.x, sc[3].x); sc[3].y = fmaf(wt, x.y, sc[3].y); }
             }
 #pragma unroll
-            for (int c = 0; c < 4; ++c) cpart[(th * 4 + c) * 128 + d] = sc[c];
-            if (d == 0) {
-#pragma unroll
-                for (int c = 0; c < 4; ++c) wspart[th][c] = wc[c];
-            }
+            for (int c = 0; c < 4; ++c) *reinterpret_cast<float2*>(qpart + (tq * 4 + c) * 128 + dp) = sc[c];
         }
         __syncthreads();
         const int c = tid >> 6, d = 2 * (tid & 63);
-        const float s0 = cpart[c * 128 + d] + cpart[(4 + c) * 128 + d];
-        const float s1 = cpart[c * 128 + d + 1] + cpart[(4 + c) * 128 + d + 1];
-        const float ws = wspart[0][c] + wspart[1][c];
+        // weight of cluster c: every warp of the cluster adds the 64 tokens in the same order
+        float ws = (lab[lane] == c ? w[lane] : 0.f) + (lab[lane + 32] == c ? w[lane + 32] : 0.f);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+        const float2 p0 = *reinterpret_cast<const float2*>(qpart + (0 * 4 + c) * 128 + d);
+        const float2 p1 = *reinterpret_cast<const float2*>(qpart + (1 * 4 + c) * 128 + d);
+        const float2 p2 = *reinterpret_cast<const float2*>(qpart + (2 * 4 + c) * 128 + d);
+        const float2 p3 = *reinterpret_cast<const float2*>(qpart + (3 * 4 + c) * 128 + d);
+        const float s0 = (p0.x + p1.x) + (p2.x + p3.x), s1 = (p0.y + p1.y) + (p2.y + p3.y);
         float c0, c1;
         if (!keep_old || ws > 0.f) {
             const float inv = 1.0f / fmaxf(ws, 1e-6f);
             c0 = s0 * inv; c1 = s1 * inv;
-            cen[c * XS + d] = c0;
-            cen[c * XS + d + 1] = c1;
+            *reinterpret_cast<float2*>(cen + c * XS + d) = make_float2(c0, c1);
         } else {
-            c0 = cen[c * XS + d]; c1 = cen[c * XS + d + 1];
+            const float2 o = *reinterpret_cast<const float2*>(cen + c * XS + d);
+            c0 = o.x; c1 = o.y;
         }
         float nn = c0 * c0 + c1 * c1;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) nn += __shfl_xor_sync(0xffffffffu, nn, o);
         if (lane == 0) wpart[warp] = nn;              // warps 2c, 2c + 1 hold cluster c
         if ((tid & 63) == 0) cw[c] = ws;
-        __syncthreads();
-        if (tid < 4) cnorm[tid] = wpart[2 * tid] + wpart[2 * tid + 1];
         __syncthreads();
     };
     update_centroids(false);
@@ -433,46 +442,70 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
             *reinterpret_cast<float4*>(dpart + (dq * 64 + tk) * 4) = make_float4(dt[0], dt[1], dt[2], dt[3]);
         }
         __syncthreads();
-        const int t = tid, c = 0;                     // threads 0 .. 63: one token each
-        int best = 0;
-        if (tid < 64) {
+        int differs = 0;
+        if (tid < 64) {                               // one token each
+            const float4 d0 = *reinterpret_cast<const float4*>(dpart + (0 * 64 + tid) * 4);
+            const float4 d1 = *reinterpret_cast<const float4*>(dpart + (1 * 64 + tid) * 4);
+            const float4 d2 = *reinterpret_cast<const float4*>(dpart + (2 * 64 + tid) * 4);
+            const float4 d3 = *reinterpret_cast<const float4*>(dpart + (3 * 64 + tid) * 4);
+            const float dot[4] = {(d0.x + d1.x) + (d2.x + d3.x), (d0.y + d1.y) + (d2.y + d3.y),
+                                  (d0.z + d1.z) + (d2.z + d3.z), (d0.w + d1.w) + (d2.w + d3.w)};
             float bd = INFINITY;
+            int best = 0;
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
-                const float dot = (dpart[(0 * 64 + t) * 4 + cc] + dpart[(1 * 64 + t) * 4 + cc]) +
-                                  (dpart[(2 * 64 + t) * 4 + cc] + dpart[(3 * 64 + t) * 4 + cc]);
-                const float dist = cw[cc] > 0.f ? cnorm[cc] - 2.0f * dot : INFINITY;
-                if (dist < bd || (cc == 0)) { if (cc == 0 || dist < bd) { bd = dist; best = cc; } }
+                const float dist = cw[cc] > 0.f ? (wpart[2 * cc] + wpart[2 * cc + 1]) - 2.0f * dot[cc] : INFINITY;
+                if (cc == 0 || dist < bd) { bd = dist; best = cc; }
             }
+            differs = tid < nvalid && best != lab[tid];
+            lab[tid] = best;                          // no other thread reads the labels in this phase
         }
-        if (tid == 0) s_changed = 0;
-        __syncthreads();
-        if (tid < 64 && c == 0 && t < nvalid && best != lab[t]) atomicAdd(&s_changed, 1);
-        __syncthreads();
-        if (tid < 64) lab[t] = best;
-        const int changed = s_changed;
-        __syncthreads();
+        const int changed = __syncthreads_or(differs);
         update_centroids(true);
         if (changed == 0) break;
     }
 
     // plain means of K and V over the final clusters, and the block means when asked for
-    if (tid < 4) {
-        int n = 0;
-        for (int t = 0; t < nvalid; ++t) n += lab[t] == tid;
-        s_cnt[tid] = (float)n;
-        c4[(size_t)h * nb4 + j * 4 + tid] = n > 0 ? log2f((float)n) : -INFINITY;
+    if (warp == 0) {
+        const int l0 = lane < nvalid ? lab[lane] : -1, l1 = lane + 32 < nvalid ? lab[lane + 32] : -1;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int n = __popc(__ballot_sync(0xffffffffu, l0 == c)) + __popc(__ballot_sync(0xffffffffu, l1 == c));
+            if (lane == c) {
+                s_cnt[c] = (float)n;
+                c4[(size_t)h * nb4 + j * 4 + c] = n > 0 ? log2f((float)n) : -INFINITY;
+            }
+        }
     }
     cp_async_wait<0>();
     __syncthreads();
     {
-        const int which = tid >> 7, d = tid & 127;
-        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int t = 0; t < nvalid; ++t) {
-            const float x = which ? __bfloat162float(sV[t * HD + d]) : __bfloat162float(sK[t * KS + d]);
+        // thread (K or V, token half, dim pair): 32 tokens, one add per (token, dim) under the uniform branch on the label
+        const int which = tid >> 7, th = (tid >> 6) & 1, dp = 2 * (tid & 63);
+        float2 sc[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sc[c] = make_float2(0.f, 0.f);
+        const __nv_bfloat16* src = which ? sV + dp : sK + dp;
+        const int stride = which ? HD : KS;
+        const int t1 = min(32 * th + 32, nvalid);
+#pragma unroll 4
+        for (int t = 32 * th; t < t1; ++t) {
             const int l = lab[t];
-            sacc[0] += l == 0 ? x : 0.f; sacc[1] += l == 1 ? x : 0.f; sacc[2] += l == 2 ? x : 0.f; sacc[3] += l == 3 ? x : 0.f;
+            const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + t * stride));
+            if (l == 0) { sc[0].x += x.x; sc[0].y += x.y; }
+            else if (l == 1) { sc[1].x += x.x; sc[1].y += x.y; }
+            else if (l == 2) { sc[2].x += x.x; sc[2].y += x.y; }
+            else { sc[3].x += x.x; sc[3].y += x.y; }
         }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) *reinterpret_cast<float2*>(qpart + ((which * 2 + th) * 4 + c) * 128 + dp) = sc[c];
+    }
+    __syncthreads();
+    {
+        const int which = tid >> 7, d = tid & 127;
+        float sacc[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) sacc[c] = qpart[((which * 2 + 0) * 4 + c) * 128 + d] + qpart[((which * 2 + 1) * 4 + c) * 128 + d];
         __nv_bfloat16* o = (which ? v4 : k4) + ((size_t)h * nb4 + j * 4) * HD + d;
 #pragma unroll
         for (int c = 0; c < 4; ++c) o[c * HD] = __float2bfloat16_rn(sacc[c] * (1.0f / fmaxf(s_cnt[c], 1.0f)));
