@@ -220,7 +220,8 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     int* lab = reinterpret_cast<int*>(w + 64);                                      // [64]
     float* dpart = reinterpret_cast<float*>(lab + 64);                              // [4 d quarters][64 tokens][4 clusters]
     // dpart is followed by 4 KB more, so that the two together hold [4][4][128] partial sums
-    __shared__ float cw[4];
+    __shared__ float cw[4], nnp[8];
+    float4* ohw = reinterpret_cast<float4*>(wpart);    // [64 tokens]: the token's weight in the slot of its cluster (wpart is dead by then)
     __shared__ float s_cnt[4];
     const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tg = lane & 3;
@@ -232,19 +233,8 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
                          metric + ((size_t)h * HD + r) * HD + c16 * 8, 16);
     }
     cp_async_commit();
-  for (int j = blockIdx.x * KM_BLOCKS; j < min(nb, (int)(blockIdx.x + 1) * KM_BLOCKS); ++j) {
-    const int nvalid = min(L - j * 64, 64);
-    __syncthreads();                       // the previous block's readers of the shared tiles are done
-    // K tile (rows past L are zero)
-    for (int e = tid; e < 64 * 16; e += 256) {
-        const int r = e >> 4, c16 = e & 15;
-        const bool okr = r < nvalid;
-        cp_async16_zfill((uint32_t)__cvta_generic_to_shared(sK + r * KS + c16 * 8),
-                         k + ((size_t)(j * 64 + (okr ? r : 0)) * H + h) * HD + c16 * 8, okr ? 16 : 0);
-    }
-    cp_async_commit();
     const int mt = warp & 3, nh = warp >> 2;
-    // this thread's A fragments of the probe scores (probes 16 mt .. +15), fetched while the K tile is in flight
+    // this thread's A fragments of the probe scores (probes 16 mt .. +15), the same for every block of the head
     uint32_t pa[8][4];
     {
         const __nv_bfloat16* p0 = probes + ((size_t)h * NP + 16 * mt + g) * HD + 2 * tg;
@@ -256,6 +246,17 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
             pa[ks][3] = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16 + 8));
         }
     }
+  for (int j = blockIdx.x * KM_BLOCKS; j < min(nb, (int)(blockIdx.x + 1) * KM_BLOCKS); ++j) {
+    const int nvalid = min(L - j * 64, 64);
+    __syncthreads();                       // the previous block's readers of the shared tiles are done
+    // K tile (rows past L are zero)
+    for (int e = tid; e < 64 * 16; e += 256) {
+        const int r = e >> 4, c16 = e & 15;
+        const bool okr = r < nvalid;
+        cp_async16_zfill((uint32_t)__cvta_generic_to_shared(sK + r * KS + c16 * 8),
+                         k + ((size_t)(j * 64 + (okr ? r : 0)) * H + h) * HD + c16 * 8, okr ? 16 : 0);
+    }
+    cp_async_commit();
     cp_async_wait<0>();
     __syncthreads();
 
@@ -353,8 +354,11 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     __syncthreads();
     if (tid < 64) {
         const float sacc = (wpart[tid] + wpart[64 + tid]) + (wpart[128 + tid] + wpart[192 + tid]);
-        w[tid] = tid < nvalid ? sacc * ((float)nvalid / (float)NP) : 0.f;
+        const float wt = tid < nvalid ? sacc * ((float)nvalid / (float)NP) : 0.f;
+        w[tid] = wt;
         lab[tid] = tid >> 4;
+        asm volatile("bar.sync 1, 64;" ::: "memory");          // warps 0 and 1 have read the partial sums that ohw overlays
+        ohw[tid] = make_float4(tid < 16 ? wt : 0.f, (tid >> 4) == 1 ? wt : 0.f, (tid >> 4) == 2 ? wt : 0.f, tid >= 48 ? wt : 0.f);
     }
     // The probe scores are dead now: their area receives the V tile (64 x 128 bf16), copied asynchronously while the
     // Lloyd iterations run, so the final cluster means do not wait on global memory.
@@ -369,10 +373,10 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     __syncthreads();
 
     // Weighted centroids of the current labels; keep_old: an emptied cluster keeps its centroid. Also the cluster weights
-    // and the squared norms of the centroids (two warp partials per cluster in wpart[0..7]).
-    // The Lloyd iterations are bound by instruction issue, so the sweep does one multiply-add per (token, dim): a token's
-    // label is the same for every thread, so the branch on it is uniform. Thread (token quarter, dim pair) sweeps 16
-    // tokens; thread (cluster, dim pair) then adds the four quarters in a fixed order.
+    // and the squared norms of the centroids (two warp partials per cluster in nnp).
+    // Thread (token quarter, dim pair) sweeps 16 tokens with the one-hot weights (no branch on the label, every load
+    // independent of the arithmetic); thread (cluster, dim pair) then adds the four quarters in a fixed order. The three
+    // warp reductions of the second phase (cluster weight, squared norm of the new and of the kept centroid) run side by side.
     float* qpart = dpart;                             // [4 token quarters][4 clusters][128]: dpart and cpart, both dead here
     auto update_centroids = [&](bool keep_old) {
         {
@@ -380,16 +384,16 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
             float2 sc[4];
 #pragma unroll
             for (int c = 0; c < 4; ++c) sc[c] = make_float2(0.f, 0.f);
-            const int t1 = min(16 * tq + 16, nvalid);
-#pragma unroll 4
-            for (int t = 16 * tq; t < t1; ++t) {
-                const int l = lab[t];
-                const float wt = w[t];
+            // tokens past the valid ones have weight zero
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const int t = 16 * tq + i;
+                const float4 o = ohw[t];
                 const float2 x = *reinterpret_cast<const float2*>(sX + t * XS + dp);
-                if (l == 0) { sc[0].x = fmaf(wt, x.x, sc[0].x); sc[0].y = fmaf(wt, x.y, sc[0].y); }
-                else if (l == 1) { sc[1].x = fmaf(wt, x.x, sc[1].x); sc[1].y = fmaf(wt, x.y, sc[1].y); }
-                else if (l == 2) { sc[2].x = fmaf(wt, x.x, sc[2].x); sc[2].y = fmaf(wt, x.y, sc[2].y); }
-                else { sc[3].x = fmaf(wt, x.x, sc[3].x); sc[3].y = fmaf(wt, x.y, sc[3].y); }
+                sc[0].x = fmaf(o.x, x.x, sc[0].x); sc[0].y = fmaf(o.x, x.y, sc[0].y);
+                sc[1].x = fmaf(o.y, x.x, sc[1].x); sc[1].y = fmaf(o.y, x.y, sc[1].y);
+                sc[2].x = fmaf(o.z, x.x, sc[2].x); sc[2].y = fmaf(o.z, x.y, sc[2].y);
+                sc[3].x = fmaf(o.w, x.x, sc[3].x); sc[3].y = fmaf(o.w, x.y, sc[3].y);
             }
 #pragma unroll
             for (int c = 0; c < 4; ++c) *reinterpret_cast<float2*>(qpart + (tq * 4 + c) * 128 + dp) = sc[c];
@@ -397,27 +401,29 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
         __syncthreads();
         const int c = tid >> 6, d = 2 * (tid & 63);
         // weight of cluster c: every warp of the cluster adds the 64 tokens in the same order
-        float ws = (lab[lane] == c ? w[lane] : 0.f) + (lab[lane + 32] == c ? w[lane + 32] : 0.f);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+        float ws = reinterpret_cast<const float*>(ohw)[4 * lane + c] + reinterpret_cast<const float*>(ohw)[4 * (lane + 32) + c];
         const float2 p0 = *reinterpret_cast<const float2*>(qpart + (0 * 4 + c) * 128 + d);
         const float2 p1 = *reinterpret_cast<const float2*>(qpart + (1 * 4 + c) * 128 + d);
         const float2 p2 = *reinterpret_cast<const float2*>(qpart + (2 * 4 + c) * 128 + d);
         const float2 p3 = *reinterpret_cast<const float2*>(qpart + (3 * 4 + c) * 128 + d);
+        const float2 old = *reinterpret_cast<const float2*>(cen + c * XS + d);
         const float s0 = (p0.x + p1.x) + (p2.x + p3.x), s1 = (p0.y + p1.y) + (p2.y + p3.y);
-        float c0, c1;
+        float nn_new = s0 * s0 + s1 * s1, nn_old = old.x * old.x + old.y * old.y;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ws += __shfl_xor_sync(0xffffffffu, ws, o);
+            nn_new += __shfl_xor_sync(0xffffffffu, nn_new, o);
+            nn_old += __shfl_xor_sync(0xffffffffu, nn_old, o);
+        }
+        float nn;
         if (!keep_old || ws > 0.f) {
             const float inv = 1.0f / fmaxf(ws, 1e-6f);
-            c0 = s0 * inv; c1 = s1 * inv;
-            *reinterpret_cast<float2*>(cen + c * XS + d) = make_float2(c0, c1);
+            *reinterpret_cast<float2*>(cen + c * XS + d) = make_float2(s0 * inv, s1 * inv);
+            nn = nn_new * (inv * inv);
         } else {
-            const float2 o = *reinterpret_cast<const float2*>(cen + c * XS + d);
-            c0 = o.x; c1 = o.y;
+            nn = nn_old;
         }
-        float nn = c0 * c0 + c1 * c1;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) nn += __shfl_xor_sync(0xffffffffu, nn, o);
-        if (lane == 0) wpart[warp] = nn;              // warps 2c, 2c + 1 hold cluster c
+        if (lane == 0) nnp[warp] = nn;                // warps 2c, 2c + 1 hold cluster c
         if ((tid & 63) == 0) cw[c] = ws;
         __syncthreads();
     };
@@ -454,11 +460,13 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
             int best = 0;
 #pragma unroll
             for (int cc = 0; cc < 4; ++cc) {
-                const float dist = cw[cc] > 0.f ? (wpart[2 * cc] + wpart[2 * cc + 1]) - 2.0f * dot[cc] : INFINITY;
+                const float dist = cw[cc] > 0.f ? (nnp[2 * cc] + nnp[2 * cc + 1]) - 2.0f * dot[cc] : INFINITY;
                 if (cc == 0 || dist < bd) { bd = dist; best = cc; }
             }
             differs = tid < nvalid && best != lab[tid];
-            lab[tid] = best;                          // no other thread reads the labels in this phase
+            lab[tid] = best;                          // no other thread reads the labels or the one-hot weights in this phase
+            const float wt = w[tid];
+            ohw[tid] = make_float4(best == 0 ? wt : 0.f, best == 1 ? wt : 0.f, best == 2 ? wt : 0.f, best == 3 ? wt : 0.f);
         }
         const int changed = __syncthreads_or(differs);
         update_centroids(true);
@@ -476,26 +484,29 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
                 c4[(size_t)h * nb4 + j * 4 + c] = n > 0 ? log2f((float)n) : -INFINITY;
             }
         }
+        // membership as 0 / 1 in place of the weights (their last readers passed the barrier that ended the iterations)
+        ohw[lane] = make_float4(l0 == 0 ? 1.f : 0.f, l0 == 1 ? 1.f : 0.f, l0 == 2 ? 1.f : 0.f, l0 == 3 ? 1.f : 0.f);
+        ohw[lane + 32] = make_float4(l1 == 0 ? 1.f : 0.f, l1 == 1 ? 1.f : 0.f, l1 == 2 ? 1.f : 0.f, l1 == 3 ? 1.f : 0.f);
     }
     cp_async_wait<0>();
     __syncthreads();
     {
-        // thread (K or V, token half, dim pair): 32 tokens, one add per (token, dim) under the uniform branch on the label
+        // thread (K or V, token half, dim pair): 32 tokens; a multiply-add with the 0 / 1 membership is an exact add
         const int which = tid >> 7, th = (tid >> 6) & 1, dp = 2 * (tid & 63);
         float2 sc[4];
 #pragma unroll
         for (int c = 0; c < 4; ++c) sc[c] = make_float2(0.f, 0.f);
         const __nv_bfloat16* src = which ? sV + dp : sK + dp;
         const int stride = which ? HD : KS;
-        const int t1 = min(32 * th + 32, nvalid);
-#pragma unroll 4
-        for (int t = 32 * th; t < t1; ++t) {
-            const int l = lab[t];
+#pragma unroll 8
+        for (int i = 0; i < 32; ++i) {
+            const int t = 32 * th + i;
+            const float4 o = ohw[t];
             const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + t * stride));
-            if (l == 0) { sc[0].x += x.x; sc[0].y += x.y; }
-            else if (l == 1) { sc[1].x += x.x; sc[1].y += x.y; }
-            else if (l == 2) { sc[2].x += x.x; sc[2].y += x.y; }
-            else { sc[3].x += x.x; sc[3].y += x.y; }
+            sc[0].x = fmaf(o.x, x.x, sc[0].x); sc[0].y = fmaf(o.x, x.y, sc[0].y);
+            sc[1].x = fmaf(o.y, x.x, sc[1].x); sc[1].y = fmaf(o.y, x.y, sc[1].y);
+            sc[2].x = fmaf(o.z, x.x, sc[2].x); sc[2].y = fmaf(o.z, x.y, sc[2].y);
+            sc[3].x = fmaf(o.w, x.x, sc[3].x); sc[3].y = fmaf(o.w, x.y, sc[3].y);
         }
 #pragma unroll
         for (int c = 0; c < 4; ++c) *reinterpret_cast<float2*>(qpart + ((which * 2 + th) * 4 + c) * 128 + dp) = sc[c];
