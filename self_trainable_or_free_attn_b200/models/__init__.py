@@ -8,12 +8,14 @@ from ..attention import EchoSparseAttention
 PRESETS = {
     "wan": dict(density=0.10, dense_steps=10, dense_layers=(0,)),
     "hunyuan_video": dict(density=0.10, dense_steps=10, dense_layers=()),
+    "minimax_h3": dict(density=0.10, dense_steps=10, dense_layers=(0,)),
 }
 
 
 def model_family(pipe):
     name = type(pipe.transformer).__name__
-    for prefix, family in (("WanTransformer", "wan"), ("HunyuanVideoTransformer", "hunyuan_video")):
+    for prefix, family in (("WanTransformer", "wan"), ("HunyuanVideoTransformer", "hunyuan_video"),
+                           ("MiniMaxH3", "minimax_h3")):
         if name.startswith(prefix):
             return family
     raise ValueError(f"unsupported transformer {name}")
@@ -37,7 +39,10 @@ def enable(pipe, preset=None, gpu="auto", **overrides):
     if family == "wan":
         from . import wan
         wan.enable(pipe, attention)
-    else:
+    elif family == "hunyuan_video":
         from . import hunyuan_video
         hunyuan_video.enable(pipe, attention)
+    else:
+        from . import minimax_h3
+        minimax_h3.enable(pipe, attention)
     return attention

@@ -84,3 +84,37 @@ def test_wan_self_attention_and_morton_hooks():
     perm, inv = common.grid_morton_order(4, 16, 16, torch.device("cuda"))
     x = torch.randn(1, 1024, 8, device="cuda")
     assert torch.equal(x.index_select(1, perm).index_select(1, inv), x)
+
+
+class _H3Transformer(torch.nn.Module):
+    def forward(self, hidden_states=None, position_ids=None, video_indices=None):
+        return hidden_states
+
+
+def test_minimax_h3_packed_sequence_on_a_fake_pipeline():
+    """[text | conditioning | audio | target video]: video rows through the sparse path (every block kept, so the result
+    must equal dense attention over the whole packed sequence), prefix rows dense, rows back in the model's order."""
+    from self_trainable_or_free_attn_b200.attention import EchoSparseAttention
+    from self_trainable_or_free_attn_b200.models import minimax_h3 as h3
+    pipe = types.SimpleNamespace(scheduler=_Sched(), transformer=_H3Transformer())
+    attn = EchoSparseAttention(density=1.0, dense_steps=2, dense_layers=(), min_blocks=1)
+    video = h3.VideoAttention(pipe, attn)
+    prefix, (f, h, w), H, D = 72, (4, 16, 16), 2, 128
+    nv = f * h * w
+    L = prefix + nv
+    pos = torch.zeros(L, 3, dtype=torch.long, device="cuda")
+    t, y, x = torch.meshgrid(torch.arange(f) * 3 + 2, torch.arange(h), torch.arange(w), indexing="ij")
+    pos[prefix:] = torch.stack([t.flatten(), y.flatten(), x.flatten()], 1).cuda()
+    video_indices = torch.cat([torch.arange(40, 56), torch.arange(prefix, L)]).cuda()
+    g = torch.Generator(device="cuda").manual_seed(0)
+    pipe.scheduler.set_timesteps(4)
+    for step in range(4):
+        pipe.transformer(hidden_states=torch.zeros(1, device="cuda"), position_ids=pos, video_indices=video_indices)
+        assert video.seq_len == L and video.layout.prefix == prefix
+        q, k, v = (torch.randn(1, L, H, D, device="cuda", generator=g).to(torch.bfloat16) for _ in range(3))
+        out = video(q, k, v)
+        ref = _dense(q, k, v)
+        err = ((out.float() - ref).norm() / ref.norm()).item()
+        assert err < 1e-2, (step, err)
+        assert video.clock.layer == 1 and video.clock.step == step
+        pipe.scheduler.step(0)

@@ -59,6 +59,9 @@ def test_presets_and_family():
     assert models.model_family(pipe) == "wan"
     assert models.settings("wan", density=0.2) == dict(density=0.2, dense_steps=10, dense_layers=(0,))
     assert models.settings("hunyuan_video")["dense_layers"] == ()
+    assert models.settings("minimax_h3") == dict(density=0.10, dense_steps=10, dense_layers=(0,))
+    WanTransformerFake.__name__ = "MiniMaxH3Transformer3DModel"
+    assert models.model_family(pipe) == "minimax_h3"
     with pytest.raises(ValueError, match="not a wan preset"):
         models.settings("wan", preset="hunyuan_video")
     pipe.transformer = torch.nn.Linear(1, 1)
@@ -77,3 +80,26 @@ def test_enable_needs_diffusers():
     WanTransformerFake.__name__ = "WanTransformer3DModel"
     with pytest.raises(ImportError):
         models.enable(pipe)
+
+
+def test_minimax_h3_layout_brings_the_target_video_to_the_front_in_morton_order():
+    """Packed sequence [text | conditioning frame | audio | target video]: the target video is the last run of
+    consecutive video positions; its rotary t coordinate is strided and must be ranked before the Morton code."""
+    from self_trainable_or_free_attn_b200.models.common import morton_order
+    from self_trainable_or_free_attn_b200.models.minimax_h3 import SequenceLayout
+    text, cond, audio, (f, h, w) = 5, 4, 3, (2, 2, 4)
+    nv = f * h * w
+    L = text + cond + audio + nv
+    pos = torch.zeros(L, 3, dtype=torch.long)
+    t, y, x = torch.meshgrid(torch.arange(f) * 4 + 7, torch.arange(h), torch.arange(w), indexing="ij")
+    start = L - nv
+    pos[start:] = torch.stack([t.flatten(), y.flatten(), x.flatten()], 1)
+    video_indices = torch.cat([torch.arange(text, text + cond), torch.arange(start, L)])
+    lay = SequenceLayout(pos, video_indices)
+    assert (lay.L, lay.prefix, lay.video) == (L, start, nv)
+    perm, _ = morton_order((t.flatten() - 7) // 4, y.flatten(), x.flatten())
+    assert torch.equal(lay.gather[:nv], perm + start) and torch.equal(lay.gather[nv:], torch.arange(start))
+    assert torch.equal(lay.gather[lay.scatter], torch.arange(L))
+    # without conditioning frames the video positions are one run
+    lay2 = SequenceLayout(pos, torch.arange(start, L))
+    assert lay2.prefix == start and lay2.matches(pos) and not lay2.matches(pos[:-1])
