@@ -83,6 +83,31 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def bind_host_to_gpu_node(device_index):
+    """Runs the calling thread on the CPUs of the NUMA node the GPU hangs off, so that the pinned host buffers it allocates
+    afterwards (first touch) sit on that node and the copies do not cross the socket link. Returns the node, or None when the
+    machine does not say (one node, no sysfs entry): host-side placement only, nothing of the GPU is changed."""
+    try:
+        bus = torch.cuda.get_device_properties(device_index).pci_bus_id
+        dev = torch.cuda.get_device_properties(device_index).pci_device_id
+        dom = torch.cuda.get_device_properties(device_index).pci_domain_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev:02x}.0/numa_node"
+        node = int(open(path).read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return None
+        os.sched_setaffinity(0, cpus)
+        return node
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None
+
+
 def inject_fallback(q, rate, scale, seed):
     """Scales Q by `scale` on a seeded random share of (tile, head) pairs, in place. Returns the number chosen."""
     _, L, H, _ = q.shape
@@ -268,6 +293,7 @@ def main():
     flagged = int(attn._states[(0, 1)].flags.sum())          # branch 0, last timed step
 
     # ---- end to end: host buffers, H2D of q, k, v and D2H of the output inside the timed region, double-buffered
+    host_node = bind_host_to_gpu_node(device.index if device.index is not None else torch.cuda.current_device())
     host_in = [[[t.cpu().pin_memory() for t in q], k.cpu().pin_memory(), v.cpu().pin_memory()] for q, k, v in inputs]
     host_out = [torch.empty(k.shape, dtype=torch.bfloat16).pin_memory() for _, k, _ in inputs]
     dev_in = [[torch.empty_like(inputs[0][1]) for _ in range(3)] for _ in range(2)]
@@ -354,7 +380,8 @@ def main():
                    "flag_threshold_log2": args.threshold},
         "clocks": clocks,
         "e2e": {"value": flops_all / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+                "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "host_numa_node": host_node},
         "gpu_launches": launches,
         "kernel_ms_per_step": {n: round(sum(timer.ms(n)) / args.steps, 3) for n in names if timer.events[n]},
         "roofline": {"bound": "tensor", "kernel": "attention_kernel<0> (es_sparse_attention)", "achieved": achieved,

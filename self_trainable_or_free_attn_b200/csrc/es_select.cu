@@ -18,24 +18,27 @@ constexpr int SEL_MAX_ITEMS = 16;           // blocks per thread: nb <= 4096 (ke
 // count). Returns 0 when fewer than K keys are non-negative, as the reference's bisection does.
 template <int ITEMS>
 __device__ int kth_largest_key(const int (&key)[ITEMS], int K, int* hist, int* bcast) {
+    // hist: two histograms of 256 bins, bcast: two result triples; pass p uses copy p & 1 and clears the other one for pass
+    // p + 1, so a pass needs two barriers (after the counting, after the digit is chosen). Both histograms are zero on
+    // entry to a pass: the caller's copies start zeroed and every call leaves them zeroed.
     const int tid = threadIdx.x;
     if (K <= 0) return 0x7F800000;            // the bisection converges to its upper end: nothing but +inf passes
     int prefix = 0, need = K;
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = 24 - 8 * pass;
-        hist[tid] = 0;
-        __syncthreads();
+        int* hs = hist + 256 * (pass & 1);
+        int* bc = bcast + 4 * (pass & 1);
         const int himask = pass == 0 ? 0 : (int)(0xFFFFFFFFu << (shift + 8));
 #pragma unroll
         for (int i = 0; i < ITEMS; ++i) {
             const int k = key[i];
-            if (k >= 0 && (k & himask) == prefix) atomicAdd(&hist[(k >> shift) & 255], 1);
+            if (k >= 0 && (k & himask) == prefix) atomicAdd(&hs[(k >> shift) & 255], 1);
         }
         __syncthreads();
         if (tid < 32) {
             // lane l owns digits 8l .. 8l+7; suffix sums from the top digit down
             int c[8], tot = 0;
-            for (int j = 0; j < 8; ++j) { c[j] = hist[8 * tid + j]; tot += c[j]; }
+            for (int j = 0; j < 8; ++j) { c[j] = hs[8 * tid + j]; hs[8 * tid + j] = 0; tot += c[j]; }
             int above = tot;                                   // inclusive suffix over lanes >= tid
             for (int o = 1; o < 32; o <<= 1) {
                 const int v = __shfl_down_sync(0xffffffffu, above, o);
@@ -49,41 +52,47 @@ __device__ int kth_largest_key(const int (&key)[ITEMS], int K, int* hist, int* b
                     if (acc + c[d] >= need) break;
                     acc += c[d];
                 }
-                bcast[0] = 8 * tid + d;
-                bcast[1] = need - acc;
+                bc[0] = 8 * tid + d;
+                bc[1] = need - acc;
             }
-            if (tid == 0) bcast[2] = above + tot;              // all matching keys
+            if (tid == 0) bc[2] = above + tot;                 // all matching keys
         }
         __syncthreads();
-        if (bcast[2] < need) return 0;                         // fewer than K non-negative keys (only at pass 0)
-        prefix |= bcast[0] << shift;
-        need = bcast[1];
-        __syncthreads();
+        if (bc[2] < need) return 0;                            // fewer than K non-negative keys (only at pass 0)
+        prefix |= bc[0] << shift;
+        need = bc[1];
     }
     return prefix;
 }
 
 // Ascending compaction of flagged elements in element order i * 256 + tid. Returns the total; `pos` gets each flagged
-// element's rank.
+// element's rank. One barrier pair for all ITEMS rounds: every warp posts its ITEMS ballot counts, then each thread adds
+// the counts of the rounds and warps before its own.
 template <int ITEMS>
 __device__ int compact_positions(const bool (&flag)[ITEMS], int (&pos)[ITEMS], int* warp_cnt) {
+    constexpr int NW = SEL_THREADS / 32;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    unsigned b[ITEMS];
+#pragma unroll
+    for (int i = 0; i < ITEMS; ++i) {
+        b[i] = __ballot_sync(0xffffffffu, flag[i]);
+        if (lane == 0) warp_cnt[i * NW + warp] = __popc(b[i]);
+    }
+    __syncthreads();
     int base = 0;
 #pragma unroll
     for (int i = 0; i < ITEMS; ++i) {
-        const unsigned b = __ballot_sync(0xffffffffu, flag[i]);
-        if (lane == 0) warp_cnt[warp] = __popc(b);
-        __syncthreads();
         int before = 0, total = 0;
-        for (int w = 0; w < SEL_THREADS / 32; ++w) {
-            const int c = warp_cnt[w];
+#pragma unroll
+        for (int w = 0; w < NW; ++w) {
+            const int c = warp_cnt[i * NW + w];
             if (w < warp) before += c;
             total += c;
         }
-        pos[i] = base + before + __popc(b & ((1u << lane) - 1u));
+        pos[i] = base + before + __popc(b[i] & ((1u << lane) - 1u));
         base += total;
-        __syncthreads();
     }
+    __syncthreads();
     return base;
 }
 
@@ -94,11 +103,14 @@ select_kernel(const float* __restrict__ map, const uint8_t* __restrict__ keep_pr
               uint8_t* __restrict__ keep_out, int* __restrict__ counts, int* __restrict__ blocks,
               const int* __restrict__ flags, int* __restrict__ bits, int nw, int* __restrict__ refine, int rw, int K,
               int R, int nb, int L, int sink, int H, int nq) {
-    __shared__ int hist[256];
-    __shared__ int bcast[4];
-    __shared__ int warp_cnt[SEL_THREADS / 32];
+    __shared__ int hist[512];
+    __shared__ int bcast[8];
+    __shared__ int warp_cnt[SEL_MAX_ITEMS * (SEL_THREADS / 32)];
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const size_t base = ((size_t)h * nq + t) * nb;
+    hist[tid] = 0;
+    hist[256 + tid] = 0;
+    __syncthreads();
     // the blocks holding the tile's own tokens, one more on each side, and the sink are always computed
     const int lo = (t * 128) / 64 - 1;
     const int hi = (min((t + 1) * 128, L) - 1) / 64 + 1;
@@ -203,7 +215,7 @@ rebuild_kernel(const int* __restrict__ exact_bits, const int* __restrict__ skip_
                uint8_t* __restrict__ keep, int* __restrict__ counts, int* __restrict__ blocks,
                int* __restrict__ refine, int rw, int* __restrict__ refine_counts, int* __restrict__ means,
                int* __restrict__ mean_counts, int nb, int nq, int H) {
-    __shared__ int warp_cnt[SEL_THREADS / 32];
+    __shared__ int warp_cnt[SEL_MAX_ITEMS * (SEL_THREADS / 32)];
     const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
     const int* ew = exact_bits + ((size_t)h * nq + t) * nw;
     const int* sw = skip_bits + ((size_t)h * nq + t) * nw;
