@@ -34,8 +34,9 @@ constexpr int BM = 128;       // query rows per tile
 constexpr int BK = 64;        // tokens per kv block
 constexpr int HD = 128;       // head dim
 constexpr int NSOFT = 256;    // softmax threads
-constexpr int NTHREADS = NSOFT + 96;
-constexpr int MMA_WARP = NSOFT / 32, LOADK_WARP = MMA_WARP + 1, LOADV_WARP = MMA_WARP + 2;
+constexpr int NTHREADS = NSOFT + 128;
+constexpr int MMA_WARP = NSOFT / 32, LOADK_WARP = MMA_WARP + 1, LOADV_WARP = MMA_WARP + 2, MASS_WARP = MMA_WARP + 3;
+constexpr int NMASS = 8;      // sets of partial block masses in flight between the softmax warps and the mass warp
 constexpr uint32_t TMEM_COLS = 512;
 constexpr uint32_t O_COL = 256, Q_COL = 384;
 constexpr int NSLOT = 6;      // K / V tiles in flight
@@ -47,19 +48,20 @@ constexpr uint32_t BLK_BYTES = BK * 128;         // 64 rows of one d half: one T
 constexpr uint32_t SMEM_RING = 0;
 constexpr uint32_t SMEM_CTL = SMEM_RING + NSLOT * TILE_BYTES;
 constexpr uint32_t SMEM_BIAS = SMEM_CTL + 3072;                        // [NBIAS][128] floats
-constexpr uint32_t SMEM_ALLOC = SMEM_BIAS + NBIAS * 128 * 4;           // 203,776 B: one CTA per SM
+constexpr uint32_t SMEM_MASS = SMEM_BIAS + NBIAS * 128 * 4;            // [NMASS][2 column halves][128 rows] floats
+constexpr uint32_t SMEM_ALLOC = SMEM_MASS + NMASS * 2 * BM * 4;        // 211,968 B: one CTA per SM
 
 struct Ctl {
     uint64_t qfull;
     uint64_t full[NSLOT], empty[NSLOT];
     uint64_t sfull[2], pfull[2];
     uint64_t ofull, drain;
-    uint64_t massbar[4], flagbar, lbar;   // softmax warps -> the thread(s) that combine their partial results
+    uint64_t massbar[NMASS], flagbar, lbar;   // softmax warps -> the thread(s) that combine their partial results
+    uint64_t massfree[NMASS];             // mass warp -> softmax warps: the set's partial sums have been read
     uint64_t sweepbar;                 // K load warp -> V load warp: the fallback sweep's tiles have all been issued
     uint32_t tmem_base;
     int abort;
     int flag_part[4];
-    float mass_part[4][2][4];          // [iteration & 3][column half][row quarter]
     float l_part[2][BM];               // row sums of the two column halves
     float m_part[2][BM];               // row maxima of the two column halves (fallback sweep)
 };
@@ -151,6 +153,21 @@ struct Sched {
     }
 };
 
+// The same order walked one iteration at a time, without the division: ph = i % p, q = i / p, o = iterations before i
+// that are not refine iterations.
+struct SchedIter {
+    int ph = 0, q = 0, o = 0;
+    __device__ __forceinline__ void get(const Sched& s, int& kind, int& idx) const {
+        if (s.nref > 0 && ph == s.p - 1 && q < s.nref) { kind = 2; idx = q; }
+        else if (o < s.n) { kind = 0; idx = o; }
+        else { kind = 1; idx = o - s.n; }
+    }
+    __device__ __forceinline__ void advance(const Sched& s) {
+        if (!(s.nref > 0 && ph == s.p - 1 && q < s.nref)) ++o;
+        if (++ph == s.p) { ph = 0; ++q; }
+    }
+};
+
 template <int MODE>
 __global__ void __launch_bounds__(NTHREADS, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
@@ -176,6 +193,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     const uint32_t sRing = base + SMEM_RING;
     volatile int* abort_flag = &ctl->abort;
     float* bias_ring = reinterpret_cast<float*>(smem_raw + SMEM_BIAS);
+    float* mass_rows = reinterpret_cast<float*>(smem_raw + SMEM_MASS);
 
     if (tid == 0) {
         if (base & 1023u) atomicCAS(a.status, 0, 901);   // the swizzled tiles need a 1024-byte aligned base
@@ -190,7 +208,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         }
         mbar_init(smem_u32(&ctl->ofull), 1);
         mbar_init(smem_u32(&ctl->drain), 1);
-        for (int i = 0; i < 4; ++i) mbar_init(smem_u32(&ctl->massbar[i]), 8);
+        for (int i = 0; i < NMASS; ++i) {
+            mbar_init(smem_u32(&ctl->massbar[i]), 8);
+            mbar_init(smem_u32(&ctl->massfree[i]), 1);
+        }
         mbar_init(smem_u32(&ctl->flagbar), 4);
         mbar_init(smem_u32(&ctl->lbar), NSOFT);
         mbar_init(smem_u32(&ctl->sweepbar), 1);
@@ -394,6 +415,31 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         if (elect_one()) umma_commit(smem_u32(&ctl->drain));
         __syncwarp();
         mbar_wait(smem_u32(&ctl->drain), 0, abort_flag, a.status, 206);
+    } else if (warp == MASS_WARP) {
+        // ------------------------------------------------------------ block masses: lane 0 / 1 = first / second block of a pair
+        if (!FALLBACK && !COMPENSATE && a.mass != nullptr) {
+            float* mrow = a.mass + ((size_t)h * a.nq + qb) * a.nb;
+            bool ok = true;
+            for (int e = 0; e < n && ok; ++e) {
+                const int set = e % NMASS, c = lane & 1;
+                const bool mine = lane < 2 && 2 * e + c < n64;
+                const int blk = mine ? __ldg(list + 2 * e + c) : 0;           // fetched before the wait
+                ok = mbar_wait_warp(smem_u32(&ctl->massbar[set]), (e / NMASS) & 1, abort_flag, a.status, 308);
+                if (!ok) break;
+                // rows lane, lane + 32, lane + 64, lane + 96 of both column halves, then the 32 lanes: always the same order
+                const float* mp = mass_rows + set * 2 * BM;
+                float m0 = (mp[lane] + mp[lane + 32]) + (mp[lane + 64] + mp[lane + 96]);
+                float m1 = (mp[BM + lane] + mp[BM + lane + 32]) + (mp[BM + lane + 64] + mp[BM + lane + 96]);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    m0 += __shfl_xor_sync(0xffffffffu, m0, o);
+                    m1 += __shfl_xor_sync(0xffffffffu, m1, o);
+                }
+                if (mine) mrow[blk] = c ? m1 : m0;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->massfree[set]));
+            }
+        }
     } else {
         // ------------------------------------------------------------ softmax and epilogue
         const int rq = warp & 3, ch = warp >> 2;             // row quarter, column half
@@ -452,36 +498,35 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         const int* bits = a.skip_bits + ((size_t)h * a.nq + qb) * a.nw;
         const bool want_mass = !FALLBACK && !COMPENSATE && a.mass != nullptr;
         const float2 sc2 = make_float2(a.scale_log2, a.scale_log2);
-        // thread 0 stores the masses of an iteration at the start of the next one: by then the other warps' partial sums
-        // have long arrived, so the store never holds back the warp that the others wait for
-        int pend_a = -1, pend_b = -1, pend_i = 0;
-        auto flush_mass = [&]() {
-            if (tid == 0 && pend_a >= 0) {
-                // one barrier and one set of partial sums per iteration modulo 4: a warp can reach iteration i + 4 only
-                // after every warp has finished iteration i + 1, so arrivals of different iterations never mix
-                if (mbar_wait(smem_u32(&ctl->massbar[pend_i & 3]), (pend_i >> 2) & 1, abort_flag, a.status, 304)) {
-                    const float* mp = ctl->mass_part[pend_i & 3][0];
-                    float* mrow = a.mass + ((size_t)h * a.nq + qb) * a.nb;
-                    mrow[pend_a] = ((mp[0] + mp[1]) + mp[2]) + mp[3];
-                    if (pend_b >= 0) mrow[pend_b] = ((mp[4] + mp[5]) + mp[6]) + mp[7];
-                }
-                pend_a = -1;
-            }
+        // kind, index and block id of an iteration are found one iteration ahead, so that the list entry (a global load)
+        // has arrived long before it is needed
+        SchedIter walk;
+        int kind = 0, idx = 0, blk = 0;
+        auto block_of = [&](int kd, int ix) -> int {
+            if (kd != 0) return 0;
+            const int e = 2 * ix + ch;
+            return __ldg(list + (e < n64 ? e : e - 1));
         };
+        if (nt > 0) {
+            walk.get(sched, kind, idx);
+            blk = block_of(kind, idx);
+        }
         for (int i = 0; i < nt && ok; ++i) {
             const int buf = i & 1;
-            int kind, idx;
-            sched.decode(i, kind, idx);
             const bool exact = kind == 0, pooled = kind == 1;
             const bool has = !exact || 2 * idx + ch < n64;
-            // block id of this warp's column half, fetched before the wait
-            const int blk = exact ? __ldg(list + (has ? 2 * idx + ch : 2 * idx + ch - 1)) : 0;
-            flush_mass();
+            const int cur_idx = idx, cur_blk = blk;
+            int nkind = 0, nidx = 0, nblk = 0;
+            walk.advance(sched);
+            if (i + 1 < nt) {
+                walk.get(sched, nkind, nidx);
+                nblk = block_of(nkind, nidx);
+            }
             // the skip words of a block-mean iteration are fetched before the wait, so that their latency is hidden by it
             uint32_t w0 = 0, w1 = 0;
             if (pooled && !COMPENSATE) {
-                w0 = (uint32_t)__ldg(bits + 4 * idx + 2 * ch);
-                w1 = (uint32_t)__ldg(bits + 4 * idx + 2 * ch + 1);
+                w0 = (uint32_t)__ldg(bits + 4 * cur_idx + 2 * ch);
+                w1 = (uint32_t)__ldg(bits + 4 * cur_idx + 2 * ch + 1);
             }
             if (tid == 0) trace_put(a.trace, 0, i, 0, t_start);
             ok = ok && mbar_wait_warp(smem_u32(&ctl->sfull[buf]), uS[buf] & 1, abort_flag, a.status, 302);
@@ -497,7 +542,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             float2 acc = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
             uint32_t pk[32];
             if (exact) {
-                int lim = (blk == a.nb - 1) ? a.tail_valid : BK;
+                int lim = (cur_blk == a.nb - 1) ? a.tail_valid : BK;
                 if (!has) lim = 0;
                 const float2 off2 = make_float2(-m, -m);
                 if (lim == BK) {
@@ -521,7 +566,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 }
             } else if (pooled) {
                 // block-mean columns: column c of this half is block 128 cv + 64 ch + c; a set bit masks it
-                const int cv = idx;
+                const int cv = cur_idx;
                 if (COMPENSATE) {
                     // every block that was not kept (refined ones included) is compensated: bits from the keep mask
                     const int b0 = 128 * cv + 64 * ch;
@@ -551,7 +596,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 }
             } else {
                 // representatives: column c of this half has the bias that the K load warp staged for this iteration
-                const int cr = idx;
+                const int cr = cur_idx;
                 const float4* bb = reinterpret_cast<const float4*>(bias_ring + (cr % NBIAS) * 128 + 64 * ch);
 #pragma unroll
                 for (int e = 0; e < 16; ++e) {
@@ -577,26 +622,21 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             acc = __fadd2_rn(acc, acc1);
             lsum = __fadd2_rn(lsum, acc);
             if (want_mass && exact) {
-                // per-block mass: this warp's 32 rows by shuffle; the four row quarters of each column half are added
-                // in a fixed order by one thread and stored (no atomics: the map is reproducible bit for bit).
-                // The partial sums are kept for four iterations: a warp can write those of iteration i + 3 only after
-                // S(i + 3) exists, which needs thread 0's pfull arrival of iteration i + 1, made after it has stored the
-                // masses of iteration i.
-                float pa = acc.x + acc.y;
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) pa += __shfl_xor_sync(0xffffffffu, pa, o);
-                if (lane == 0) {
-                    ctl->mass_part[idx & 3][ch][rq] = pa;
-                    mbar_arrive(smem_u32(&ctl->massbar[idx & 3]));
+                // per-block mass: every row leaves its sum over the block's columns in shared memory; the mass warp adds
+                // the 128 rows in a fixed order and stores the result (no atomics: the map is reproducible bit for bit). A
+                // set of row sums is written again NMASS exact iterations later, once the mass warp has handed it back.
+                const int set = cur_idx % NMASS, round = cur_idx / NMASS;
+                if (round > 0) {
+                    ok = mbar_wait_warp(smem_u32(&ctl->massfree[set]), (round - 1) & 1, abort_flag, a.status, 304);
+                    if (!ok) break;
                 }
-                if (tid == 0) {
-                    pend_a = blk;
-                    pend_b = (2 * idx + 1 < n64) ? list[2 * idx + 1] : -1;
-                    pend_i = idx;                      // slots and barrier phases count the exact iterations
-                }
+                mass_rows[(set * 2 + ch) * BM + trow] = acc.x + acc.y;      // this row's sum over the block's 64 columns
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&ctl->massbar[set]));
             }
+            if (tid == 0) trace_put(a.trace, 0, i, 5, t_start);
+            kind = nkind; idx = nidx; blk = nblk;
         }
-        if (ok) flush_mass();
 
         // ---- epilogue: row sums of both column halves, then this thread's 64 columns of O
         ctl->l_part[ch][trow] = lsum.x + lsum.y;

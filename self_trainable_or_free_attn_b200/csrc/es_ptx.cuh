@@ -44,6 +44,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// The non-blocking test of the same phase: it answers at once, where try_wait may first suspend the thread for a while.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // Wait limit of every barrier wait in this library: far above any legitimate wait (a CTA lives for well under a
 // second), short enough that a stuck pipeline returns quickly.
 constexpr uint64_t kWaitLimitNs = 500000000ull;
@@ -70,7 +83,14 @@ __device__ __forceinline__ void dbg_timeout(int) {}
 // once. The device status word is checked too, so once one CTA has given up the others stop waiting as well and the
 // kernel ends quickly instead of after one time limit per CTA.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
+                                          int code, int spins = 0) {
+    if (mbar_test_wait(bar, parity)) return true;      // the common case: the phase is already complete
+    // `spins` > 0: poll with the non-blocking test first. A thread suspended in try_wait was seen to resume 400 to 600
+    // clocks after the phase completed; a polling one sees it within a round trip to the barrier, but takes issue slots
+    // from the warps that compute, so only the warp that everything else waits for (the MMA issuer) asks for it.
+#pragma unroll 1
+    for (int spin = 0; spin < spins; ++spin)
+        if (mbar_test_wait(bar, parity)) return true;
     if (mbar_try_wait(bar, parity)) return true;
     const int64_t t0 = (int64_t)global_timer_ns();
     uint32_t polls = 0, late = 0;
@@ -99,8 +119,8 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 // The same wait for code that the whole warp runs together and that uses warp-wide instructions afterwards (elect,
 // shuffles, votes): every lane gets the same answer, false as soon as one lane gave up.
 __device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                               int code) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code)) != 0;
+                                               int code, int spins = 0) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code, spins)) != 0;
 }
 
 // One lane of a converged warp: true for exactly one of the 32 lanes. Code that is otherwise warp-uniform and issues a
