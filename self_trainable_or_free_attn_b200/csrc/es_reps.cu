@@ -132,8 +132,16 @@ metric_kernel(const float* __restrict__ parts, __nv_bfloat16* __restrict__ metri
     __shared__ float s_eps, s_diag;
     const int h = blockIdx.x, tid = threadIdx.x;
     for (int e = tid; e < HD * HD; e += 256) {
-        float s = 0.f;
-        for (int p = 0; p < nsplit; ++p) s += parts[((size_t)h * nsplit + p) * HD * HD + e];
+        // four running sums over the splits p % 4 (independent loads in flight), combined in a fixed order
+        float s4[4] = {0.f, 0.f, 0.f, 0.f};
+        const float* src = parts + (size_t)h * nsplit * HD * HD + e;
+        int p = 0;
+        for (; p + 4 <= nsplit; p += 4) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) s4[u] += src[(size_t)(p + u) * HD * HD];
+        }
+        for (int u = 0; p < nsplit; ++p, ++u) s4[u] += src[(size_t)p * HD * HD];
+        const float s = (s4[0] + s4[1]) + (s4[2] + s4[3]);
         A[(e >> 7) * 129 + (e & 127)] = s * norm;
         Lm[(e >> 7) * 129 + (e & 127)] = 0.f;
     }
@@ -166,10 +174,15 @@ metric_kernel(const float* __restrict__ parts, __nv_bfloat16* __restrict__ metri
             Lm[tid * 129 + j] = v;
         }
         __syncthreads();
-        // A -= lj lj^T on the trailing block (rows / columns before j have lj = 0)
-        for (int e = tid; e < HD * HD; e += 256) {
-            const int r = e >> 7, c = e & 127;
-            if (r >= j && c >= j) A[r * 129 + c] -= lj[r] * lj[c];
+        // A -= lj lj^T on the lower triangle of the trailing block, the only part later columns read: two threads per
+        // row r > j, columns j + 1 .. r alternating between them
+        {
+            const int r = tid >> 1;
+            if (r > j) {
+                const float lr = lj[r];
+                float* row = A + r * 129;
+                for (int c = j + 1 + (tid & 1); c <= r; c += 2) row[c] -= lr * lj[c];
+            }
         }
         __syncthreads();
     }
