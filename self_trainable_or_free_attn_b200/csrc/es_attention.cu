@@ -180,6 +180,20 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     // adjacent CTAs are adjacent query tiles of one head: their kv lists overlap in L2
     const int qb = blockIdx.x % a.nq, h = blockIdx.x / a.nq;
     const int th_idx = qb * a.H + h;
+    // The tile's first global loads do not depend on one another: the list length, the first window of block ids (load
+    // warps) and this thread's half of its Q row (softmax warps) are requested here, before the status check, the barrier
+    // set-up and the tensor-memory allocation, whose latencies they then share instead of following them.
+    const int n64_early = COMPENSATE ? 0 : __ldg(a.counts + th_idx);
+    int win_early = 0;
+    uint4 q_early[8];
+    if (warp == LOADK_WARP || warp == LOADV_WARP) {
+        if (!COMPENSATE && lane < a.nk) win_early = __ldg(a.blocks + (size_t)th_idx * a.nk + lane);
+    } else if (warp < NSOFT / 32) {
+        const int r0 = qb * BM + 32 * (warp & 3) + lane;
+        const uint4* src = reinterpret_cast<const uint4*>(a.q + ((size_t)(r0 < a.L ? r0 : 0) * a.H + h) * HD + 64 * (warp >> 2));
+#pragma unroll
+        for (int i = 0; i < 8; ++i) q_early[i] = r0 < a.L ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+    }
     if (FALLBACK || COMPENSATE) {
         if (a.flags[th_idx] == 0) return;          // uniform over the CTA, before anything is allocated
     }
@@ -229,7 +243,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     const uint32_t tmem = ctl->tmem_base;
     if (tid == 0) dbg_stage(2);
 
-    const int n64 = COMPENSATE ? 0 : a.counts[th_idx];
+    const int n64 = n64_early;
     const int n = (n64 + 1) >> 1;                     // exact iterations: pairs of 64-token blocks
     const int nvirt = FALLBACK ? 0 : a.nvirt;
     const int nref = (FALLBACK || COMPENSATE) ? 0 : a.nref;
@@ -255,7 +269,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         const uint32_t box_off = (uint32_t)(lane >> 1) * HALF_BYTES + (uint32_t)(lane & 1) * BLK_BYTES;   // lanes 0..3
         const int box_x = (lane >> 1) * 64;
         // block ids: a 32-entry window of the list held across the lanes, one coalesced load per 16 iterations
-        int win = 0, wbase = -1;
+        int win = lane < n64 ? win_early : 0, wbase = 0;       // the first window was requested at the top of the kernel
         // tile number `seq` of the ring: K or V tile of iteration i (i < 0: K tile -i-1 of the fallback sweep)
         auto put = [&](uint32_t seq, int i) {
             if (!ok) return;
@@ -451,10 +465,9 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 
         // this thread's half of its Q row -> tensor memory (bf16 pairs, 32 columns), the A operand of every QK^T
         {
-            const uint4* src = reinterpret_cast<const uint4*>(a.q + ((size_t)(valid ? row : 0) * a.H + h) * HD + 64 * ch);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                uint4 w = valid ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
+                const uint4 w = q_early[i];
                 s[4 * i] = w.x; s[4 * i + 1] = w.y; s[4 * i + 2] = w.z; s[4 * i + 3] = w.w;
             }
             tmem_st32(lane_base + Q_COL + 32 * ch, s);
