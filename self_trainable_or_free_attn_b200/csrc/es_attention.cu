@@ -180,9 +180,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     // adjacent CTAs are adjacent query tiles of one head: their kv lists overlap in L2
     const int qb = blockIdx.x % a.nq, h = blockIdx.x / a.nq;
     const int th_idx = qb * a.H + h;
+    if (FALLBACK || COMPENSATE) {
+        if (a.flags[th_idx] == 0) return;          // uniform over the CTA, before anything is allocated
+    }
     // The tile's first global loads do not depend on one another: the list length, the first window of block ids (load
-    // warps) and this thread's half of its Q row (softmax warps) are requested here, before the status check, the barrier
-    // set-up and the tensor-memory allocation, whose latencies they then share instead of following them.
+    // warps) and this thread's half of its Q row (softmax warps) are requested here (in the fallback modes: once the tile
+    // is known to be flagged), before the status check, the barrier set-up and the tensor-memory allocation, whose
+    // latencies they then share instead of following them.
     const int n64_early = COMPENSATE ? 0 : __ldg(a.counts + th_idx);
     int win_early = 0;
     uint4 q_early[8];
@@ -193,9 +197,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         const uint4* src = reinterpret_cast<const uint4*>(a.q + ((size_t)(r0 < a.L ? r0 : 0) * a.H + h) * HD + 64 * (warp >> 2));
 #pragma unroll
         for (int i = 0; i < 8; ++i) q_early[i] = r0 < a.L ? __ldg(src + i) : make_uint4(0, 0, 0, 0);
-    }
-    if (FALLBACK || COMPENSATE) {
-        if (a.flags[th_idx] == 0) return;          // uniform over the CTA, before anything is allocated
     }
     // a wait has given up earlier (the status word is set until the host reads it): do not start more work
     if (*reinterpret_cast<volatile int*>(a.status) != 0) return;
