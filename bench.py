@@ -1,15 +1,20 @@
-"""Benchmark of the EchoSparse sparse-step attention layer on B200.
+"""Benchmark of the two hot paths on B200: the EchoSparse sparse-step attention layer and the VSA2 training layer.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-A step is one sparse-step attention layer: both CFG branches through `EchoSparseAttention.__call__` (select, block
-means, representatives, fused sparse attention, fallback, estimates). Default workload: the Wan2.1-14B 720p shape
-(2 branches x 40 heads x 75,600 tokens, 10 % of the blocks kept, ~0.5 % of the tiles pushed into the online-softmax
-fallback). With N GPUs the heads are sharded (both branches of a head on one GPU), no collective in the data path.
-Rank 0 prints one JSON line. Inputs are seeded synthetic activations (see `synthetic.py`).
+EchoSparse workloads (default `wan_14b_720p`: 2 CFG branches x 40 heads x 75,600 tokens, 10 % of the blocks kept, ~0.5 % of
+the tiles pushed into the online-softmax fallback): a step is one sparse-step attention layer, both CFG branches through
+`EchoSparseAttention.__call__` (plan -> lists, block means, representatives, fused sparse attention, fallback, estimates,
+next plan). With N GPUs the heads are sharded (both branches of a head on one GPU), no collective in the data path.
+`--heads H` keeps only the first H heads (a small case for a profiler).
 
-`--impl reference` times the CPU restatement of the same step (oracle/echosparse_ref.py) on the host cores, on a bounded
-sample of query tiles of the same workload.
+`--workload vsa2_train` (B = 1, 12 heads, 32,768 tokens of a 16 x 32 x 64 grid, top-k 32): a step is one forward + backward
+of `vsa2_attention` on a frozen selection; `--skew CASE` picks the shape of the selection (`tenth_x4`: 10 % of the query
+blocks select 4 x more kv blocks), `--split none|auto|manual` the split-KV scheduling.
+
+Rank 0 prints one JSON line. Inputs are seeded synthetic activations (`synthetic.py`, `vsa/workloads.py`).
+`--impl reference` times the CPU restatement of the same step (oracle/) on the host cores, on a bounded sample of the same
+workload.
 """
 import argparse
 import json
@@ -37,8 +42,27 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             d = json.load(f)
-        return {"tflops": float(d["bf16_tflops_sustained"]), "hbm_gbs": float(d["hbm_gbs"]), "source": "measured"}
-    return {"tflops": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+        return {"burst": float(d["bf16_tflops"]), "sustained": float(d["bf16_tflops_sustained"]),
+                "hbm_gbs": float(d["hbm_gbs"]), "sm_max_mhz": float(d.get("sm_max_mhz", 1965.0)), "source": "measured"}
+    return {"burst": 1590.0, "sustained": 1400.0, "hbm_gbs": 6650.0, "sm_max_mhz": 1965.0, "source": "fallback"}
+
+
+NOMINAL_BF16_TFLOPS = 2250.0      # dense bf16 at the maximum SM clock
+
+
+def tensor_roofline(kernel, achieved, ms, launches, clocks, peaks, **more):
+    """The roofline object of a tensor-core-bound kernel. `frac` is against the burst peak (a cuBLAS GEMM timed alone, the
+    comparable figure for a kernel that runs tens of milliseconds at full clocks); the sustained-peak fraction and the
+    fraction of the nominal pipe rate at the SM clock sampled during the run stand beside it."""
+    sm = clocks.get("sm_mhz") or peaks["sm_max_mhz"]
+    pipe = NOMINAL_BF16_TFLOPS * sm / peaks["sm_max_mhz"]
+    out = {"bound": "tensor", "kernel": kernel, "achieved": achieved, "peak": peaks["burst"], "unit": "TFLOP/s",
+           "frac": achieved / peaks["burst"], "peak_source": f"bf16_tflops (burst) of {peaks['source']}",
+           "frac_of_sustained": achieved / peaks["sustained"], "peak_sustained": peaks["sustained"],
+           "frac_of_pipe_at_sampled_clock": achieved / pipe, "pipe_peak_at_sampled_clock": pipe,
+           "ms_per_launch": ms, "launches_timed": launches}
+    out.update(more)
+    return out
 
 
 class ClockSampler:
@@ -119,6 +143,20 @@ def inject_fallback(q, rate, scale, seed):
     return len(pick)
 
 
+def workload_config(args, world=1):
+    """The keys both arms print under `config`: what the workload is, not how an arm runs it."""
+    grid, heads_all, branches, density, text = synthetic.WORKLOADS[args.workload]
+    heads = min(args.heads, heads_all) if args.heads else heads_all
+    return {"workload": args.workload, "tokens": synthetic.grid_tokens(grid) + text, "heads": heads, "branches": branches,
+            "density": density, "head_dim": 128, "flag_threshold_log2": args.threshold,
+            "partition": (f"heads over {world} GPU(s), both CFG branches of a head together"
+                          + ("; sequence-sharded caller: q, k, v and the output cross the ranks by NCCL all-to-all every step "
+                             "(Ulysses)" if args.ulysses and world > 1 else "")),
+            "l2": "inputs (q, k, v of a branch >> 126 MB) exceed L2 between iterations",
+            "step": "one sparse-step attention layer, both CFG branches: plan -> lists, block means, representatives, fused "
+                    "sparse attention, fallback of flagged tiles, estimates, next plan"}
+
+
 def sink_of(workload):
     """First kv block of the text tokens (always computed), or None: hunyuan_video.py:66 of the reference."""
     grid, _, _, _, text = synthetic.WORKLOADS[workload]
@@ -131,9 +169,9 @@ def build_job(args, rank, world, device):
     from self_trainable_or_free_attn_b200.attention import EchoSparseAttention
     grid, heads_all, branches, density, text = synthetic.WORKLOADS[args.workload]
     cid = CONFIG_IDS[args.workload]
-    heads = synthetic.shard_heads(heads_all, rank, world)
+    heads = synthetic.shard_heads(min(args.heads, heads_all) if args.heads else heads_all, rank, world)
     attn = EchoSparseAttention(density=density, dense_steps=2, dense_layers=(), refine_iters=6,
-                               threshold=args.threshold, min_blocks=1)
+                               threshold=args.threshold, min_blocks=1, state=args.state)
     for b in range(branches):
         qp, kp, vp = synthetic.branch_qkv(grid, cid, b, heads, device, text, prev=True)
         attn(qp, kp, vp, 0, b, layer=1, sink=sink_of(args.workload))    # dense: log2 LSE of the perturbed inputs -> offset
@@ -194,13 +232,222 @@ def reference_arm(args, threads):
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": nominal / (value * 1e12) * 1e3 if nominal else None, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.workload, "tokens": synthetic.grid_tokens(grid) + text, "heads": heads_all,
-                       "branches": branches, "density": density,
-                       "step": "fused sparse step on host cores; ms_per_step extrapolates the sample's throughput to the "
-                               "layer's nominal algorithmic FLOP"},
+            "config": workload_config(args, args.gpus),
+            "how": "fused sparse step of a sample of query tiles on the host cores; ms_per_step extrapolates the sample's "
+                   "throughput to the layer's nominal algorithmic FLOP",
             "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------------------ VSA2
+VSA2_SHAPE = dict(grid=(16, 32, 64), heads=12, topk=32)
+
+
+def vsa2_config(args, world=1):
+    sh = VSA2_SHAPE
+    heads = min(args.heads, sh["heads"]) if args.heads else sh["heads"]
+    g = sh["grid"]
+    return {"workload": "vsa2_train", "tokens": g[0] * g[1] * g[2], "heads": heads, "head_dim": 128, "tile": 64,
+            "topk": sh["topk"], "selection": args.skew, "split_kv": args.split,
+            "step": "forward + backward of vsa2_attention (fine block-sparse + coarse block-mean attention, tanh gate) on a "
+                    "frozen selection: O, dQ, dK, dV, dgate",
+            "partition": f"heads over {world} GPU(s), no collective (every kernel is per head)",
+            "l2": "q, k, v, dO, O and the gradients of one step (>= 0.8 GB at 12 heads) exceed L2 between iterations"}
+
+
+def vsa2_reference_arm(args, threads):
+    """The sampled float32 CPU oracle (oracle/vsa_sampled.py) on the host cores: per step, forward and gradients of a
+    sample of query blocks and kv blocks of one head; throughput on the algorithmic FLOP of what it evaluated."""
+    from oracle.vsa_sampled import SampledVSA2
+    from self_trainable_or_free_attn_b200.vsa import workloads
+    sh = VSA2_SHAPE
+    torch.set_num_threads(threads)
+    q, k, v, gate, dout, lay = workloads.train_inputs(sh["grid"], 1, device="cpu")
+    mask = workloads.selection_mask(args.skew, sh["grid"], 1, sh["topk"])[0, 0]
+    nb = mask.shape[0]
+    q2k = [mask[i].nonzero().flatten().tolist() for i in range(nb)]
+    k2q = [mask[:, j].nonzero().flatten().tolist() for j in range(nb)]
+    blocks = list(range(0, nb, 4))                         # a quarter of the query blocks and of the kv blocks
+
+    def one_pass():
+        ora = SampledVSA2(q[0, 0], k[0, 0], v[0, 0], gate[0, 0], dout[0, 0], lay.blk_cnt, q2k, k2q)
+        t0 = time.perf_counter()
+        rows = set()
+        for i in blocks:
+            ora.query_block(i)
+            rows.add(i)
+        pairs_kv = 0
+        for j in blocks:
+            ora.kv_block(j)
+            rows.update(k2q[j])
+            pairs_kv += len(k2q[j])
+        dt = time.perf_counter() - t0
+        # forward of every row touched (2 products per pair), dQ of the sampled rows (3), dK / dV of the sampled blocks (4)
+        pairs_fwd = sum(len(q2k[i]) for i in rows)
+        pairs_q = sum(len(q2k[i]) for i in blocks)
+        flop = 2.0 * 64 * 64 * 128 * (2 * pairs_fwd + 3 * pairs_q + 4 * pairs_kv)
+        return flop / dt / 1e12, dt
+
+    vals = [one_pass()[0] for _ in range(args.warmup + args.steps)][args.warmup:]
+    value = statistics.median(vals)
+    nominal = 3.5 * 4.0 * 64 * 64 * 128 * nb * sh["topk"] * sh["heads"]
+    sample = (f"{len(blocks)} of {nb} query blocks (O, LSE, dQ, dgate) and {len(blocks)} of {nb} kv blocks (dK, dV) of one head, "
+              f"closed-form float32 (oracle/vsa_sampled.py), selection {args.skew}")
+    line = {"impl": "reference", "metric": "vsa2_fwd_bwd_effective_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": nominal / (value * 1e12) * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": vsa2_config(args, args.gpus),
+            "how": "sampled blocks on the host cores; ms_per_step extrapolates the sample's throughput to the layer's "
+                   "algorithmic FLOP",
+            "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def vsa2_arm(args, rank, world, local, threads):
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA GPU; there is no CPU fallback of the product path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    from self_trainable_or_free_attn_b200 import _native, vsa
+    from self_trainable_or_free_attn_b200.vsa import ops, workloads
+    sh = VSA2_SHAPE
+    heads_all = min(args.heads, sh["heads"]) if args.heads else sh["heads"]
+    mine = synthetic.shard_heads(heads_all, rank, world)
+    if not mine:
+        raise SystemExit(f"{world} ranks for {heads_all} heads: a rank without a head")
+    q, k, v, gate, dout, lay = workloads.train_inputs(sh["grid"], heads_all, device="cpu")
+    q, k, v, gate, dout = (x[:, mine].contiguous().to(device) for x in (q, k, v, gate, dout))
+    cnt = lay.blk_cnt.to(device)
+    mask = workloads.selection_mask(args.skew, sh["grid"], heads_all, sh["topk"])[:, mine]
+    sel = ops.mask_to_selection(mask.to(device))
+    split = {"none": None, "auto": vsa.SplitKV.auto(), "manual": vsa.SplitKV(chunk=64)}[args.split]
+    fwd_flop, bwd_flop, pairs = workloads.fine_flops(sel)
+    rows = sel.row_counts().reshape(-1)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(qq, kk, vv, gg, dd):
+        leaves = [x.detach().requires_grad_(True) for x in (qq, kk, vv, gg)]
+        o = vsa.vsa2_attention(*leaves, cnt, R=16, selection=sel, split_kv=split)
+        return (o.detach(),) + torch.autograd.grad(o, leaves, dd)
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    for _ in range(args.warmup):
+        step(q, k, v, gate, dout)
+    launches0 = _native.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step(q, k, v, gate, dout)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    launches = _native.launch_count() - launches0
+    # the fine kernels alone (CUDA events on the launching stream), same inputs
+    def timed(fn, n=5):
+        fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            out = fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n, out
+    ms_f, (of, lse) = timed(lambda: ops.attn_fwd(q, k, v, sel.q2k_ptr, sel.q2k_idx, cnt))
+    delta = (dout.float() * of.float()).sum(-1)
+    ms_kv, _ = timed(lambda: ops._bwd_kv(q, k, v, dout, lse, delta, sel.k2q_ptr, sel.k2q_idx, cnt))
+    ms_q, _ = timed(lambda: ops._bwd_q(q, k, v, dout, lse, delta, sel.q2k_ptr, sel.q2k_idx, cnt))
+    extra = 0
+    while sampler.count() < 3 and extra < 200:
+        step(q, k, v, gate, dout)
+        torch.cuda.synchronize()
+        extra += 1
+    clocks = sampler.stop()
+    clocks["window"] = "warm-up + timed steps + kernel timings" + (f" + {extra} more steps" if extra else "")
+    # ---- end to end: host buffers in, results out, every step
+    ms_e2e, h2d, d2h = float("nan"), 0, 0
+    if not args.no_e2e:
+        host = [x.cpu().pin_memory() for x in (q, k, v, gate, dout)]
+        dev = [torch.empty_like(x) for x in (q, k, v, gate, dout)]
+        back = [torch.empty(x.shape, dtype=x.dtype).pin_memory() for x in (q, q, k, v, gate)]
+
+        def e2e_step():
+            for d, h in zip(dev, host):
+                d.copy_(h, non_blocking=True)
+            for b, r in zip(back, step(*dev)):
+                b.copy_(r, non_blocking=True)
+        e2e_step()
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+        h2d = sum(x.numel() * x.element_size() for x in host)
+        d2h = sum(x.numel() * x.element_size() for x in back)
+    status = _native.device_status()
+    stats = torch.tensor([ms, ms_e2e, fwd_flop + bwd_flop, float(launches), float(h2d), float(d2h), float(status), ms_f,
+                          ms_kv + ms_q], device=device, dtype=torch.float64)
+    flop_rank = fwd_flop + bwd_flop
+    if dist is not None:
+        mx, sm = stats.clone(), stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        ms, ms_e2e, status = float(mx[0]), float(mx[1]), int(mx[6])
+        flop_all, launches, h2d, d2h = float(sm[2]), int(sm[3]), int(sm[4]), int(sm[5])
+    else:
+        flop_all = flop_rank
+    if rank != 0:
+        dist.destroy_process_group()
+        return
+    if status != 0:
+        raise SystemExit(f"a kernel reported status {status}; the numbers are void")
+    peaks = measured_peaks()
+    ms_step = ms / args.steps
+    fwd_tf, bwd_tf = fwd_flop / ms_f / 1e9, bwd_flop / (ms_kv + ms_q) / 1e9
+    line = {
+        "metric": "vsa2_fwd_bwd_effective_tflops", "value": flop_all / ms_step / 1e9, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": vsa2_config(args, world),
+        "run": {"pairs_per_rank": pairs, "list_length_mean": float(rows.float().mean()), "list_length_max": int(rows.max()),
+                "algorithmic_tflop_per_step": flop_all / 1e12,
+                "flop_rule": "fine branch only: forward 4*64*64*D per selected pair, backward 2.5 x (five products per pair)"},
+        "clocks": clocks,
+        "e2e": None if args.no_e2e else {"value": flop_all / (ms_e2e / args.steps) / 1e9, "unit": "TFLOP/s",
+                                         "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d,
+                                         "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "kernel_ms": {"fine_forward": round(ms_f, 4), "fine_backward_kv": round(ms_kv, 4), "fine_backward_q": round(ms_q, 4)},
+        "roofline": tensor_roofline("fine forward kernel (es_vsa_attn_fwd)", fwd_tf, ms_f, 5, clocks, peaks, traffic=None),
+        "roofline_backward": tensor_roofline("fine backward kernels (es_vsa_attn_bwd_kv + es_vsa_attn_bwd_q)", bwd_tf,
+                                             ms_kv + ms_q, 5, clocks, peaks, traffic=None),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        from types import SimpleNamespace
+        import contextlib
+        import io
+        buf = io.StringIO()
+        with contextlib.redirect_stdout(buf):
+            vsa2_reference_arm(SimpleNamespace(skew=args.skew, split=args.split, heads=args.heads, gpus=1, steps=1, warmup=0),
+                               threads)
+        line["cpu_baseline"] = json.loads(buf.getvalue())["cpu_baseline"]
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
 
 
 def main():
@@ -209,7 +456,12 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="wan_14b_720p", choices=sorted(synthetic.WORKLOADS))
+    ap.add_argument("--workload", default="wan_14b_720p", choices=sorted(synthetic.WORKLOADS) + ["vsa2_train"])
+    ap.add_argument("--heads", type=int, default=0, help="use only the first N heads of the workload (0 = all)")
+    ap.add_argument("--state", default="compact", choices=["compact", "layer"], help="what a layer keeps between steps")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end to end) measurement")
+    ap.add_argument("--skew", default="uniform", help="vsa2_train: shape of the selection (vsa/workloads.py CASES)")
+    ap.add_argument("--split", default="none", choices=["none", "auto", "manual"], help="vsa2_train: split-KV scheduling")
     ap.add_argument("--threshold", type=float, default=60.0, help="flag threshold on |log2 row sum| (reference: 60)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -224,8 +476,10 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference" and rank != 0:
         return
-    grid, heads_all, branches, density, text = synthetic.WORKLOADS[args.workload]
     threads = os.cpu_count() or 1
+    if args.workload == "vsa2_train":
+        return vsa2_reference_arm(args, threads) if args.impl == "reference" else vsa2_arm(args, rank, world, local, threads)
+    grid, heads_all, branches, density, text = synthetic.WORKLOADS[args.workload]
     if args.impl == "reference":
         return reference_arm(args, threads)
     if not torch.cuda.is_available():
@@ -266,7 +520,7 @@ def main():
     sampler.start()
     run_steps(attn_call, inputs, 2, args.warmup, sink)
     names = ["sparse_attention", "block_attention", "exact_fallback", "compensate_fallback", "block_means", "select_blocks",
-             "estimate_skipped", "full_step_scales", "reps_build"]
+             "estimate_skipped", "full_step_scales", "reps_build", "pack_plan", "rebuild_plan"]
     timer = K.KernelTimer(names)
     barrier()
     K.set_kernel_timer(timer)
@@ -288,15 +542,16 @@ def main():
     clocks = sampler.stop()
     clocks["window"] = "warm-up + timed steps" + (f" + {extra} more steps of the same load" if extra else "")
     kernel_ms = timer.ms("sparse_attention")
-    status = _native.device_status()
     flops_rank = layer_flops(attn, inputs, L)
-    flagged = int(attn._states[(0, 1)].flags.sum())          # branch 0, last timed step
+    flagged = int(attn._states[(0, 1)].flags.sum())          # last call of the timed steps (the last branch)
 
     # ---- end to end: host buffers, H2D of q, k, v and D2H of the output inside the timed region, double-buffered
-    host_node = bind_host_to_gpu_node(device.index if device.index is not None else torch.cuda.current_device())
-    host_in = [[[t.cpu().pin_memory() for t in q], k.cpu().pin_memory(), v.cpu().pin_memory()] for q, k, v in inputs]
-    host_out = [torch.empty(k.shape, dtype=torch.bfloat16).pin_memory() for _, k, _ in inputs]
-    dev_in = [[torch.empty_like(inputs[0][1]) for _ in range(3)] for _ in range(2)]
+    host_node, host_in, host_out, dev_in = None, None, None, None
+    if not args.no_e2e:
+        host_node = bind_host_to_gpu_node(device.index if device.index is not None else torch.cuda.current_device())
+        host_in = [[[t.cpu().pin_memory() for t in q], k.cpu().pin_memory(), v.cpu().pin_memory()] for q, k, v in inputs]
+        host_out = [torch.empty(k.shape, dtype=torch.bfloat16).pin_memory() for _, k, _ in inputs]
+        dev_in = [[torch.empty_like(inputs[0][1]) for _ in range(3)] for _ in range(2)]
     copy_stream = torch.cuda.Stream()           # host -> device
     back_stream = torch.cuda.Stream()           # device -> host: its own stream, PCIe carries both directions at once
     main_stream = torch.cuda.current_stream()
@@ -326,13 +581,26 @@ def main():
         main_stream.wait_stream(copy_stream)
         main_stream.wait_stream(back_stream)
 
-    e2e_steps(2 + args.warmup + args.steps, 1)
-    barrier()
+    ms_e2e = float("nan")
+    if not args.no_e2e:
+        e2e_steps(2 + args.warmup + args.steps, 1)
+        barrier()
+        e0.record()
+        e2e_steps(3 + args.warmup + args.steps, args.steps)
+        e1.record()
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
+    # one dense step (online softmax over every block, what the first dense_steps - 1 steps of a video run), branch 0
+    attn.reset()
+    q0, k0, v0 = inputs[0]
+    attn_call(q0[0], k0, v0, 0, 0, layer=1, sink=sink)
+    torch.cuda.synchronize()
     e0.record()
-    e2e_steps(3 + args.warmup + args.steps, args.steps)
+    attn_call(q0[0], k0, v0, 0, 0, layer=1, sink=sink)
     e1.record()
-    barrier()
-    ms_e2e = e0.elapsed_time(e1)
+    torch.cuda.synchronize()
+    ms_dense = e0.elapsed_time(e1)
+    status = _native.device_status()
     h2d = sum(3 * k.numel() * 2 for _, k, _ in inputs)
     d2h = sum(k.numel() * 2 for _, k, _ in inputs)
 
@@ -369,28 +637,20 @@ def main():
         "metric": "sparse_attn_effective_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": args.workload, "tokens": L, "heads": heads_all, "branches": branches, "density": density,
-                   "partition": (f"heads over {world} GPU(s), both CFG branches of a head together"
-                                 + ("; sequence-sharded caller: q, k, v and the output cross the ranks by NCCL all-to-all every "
-                                    "step (Ulysses)" if args.ulysses and world > 1 else "")),
-                   "step": "select + block means + representatives + fused sparse attention + fallback + estimates, "
-                           "both branches", "algorithmic_tflop_per_step": flops_all / 1e12,
-                   "l2": "inputs (q, k, v of a branch >> 126 MB) exceed L2 between iterations",
-                   "fallback_tiles_injected": injected, "fallback_tiles_flagged_last_step_branch0": flagged,
-                   "flag_threshold_log2": args.threshold},
+        "config": workload_config(args, world),
+        "run": {"state": args.state, "algorithmic_tflop_per_step": flops_all / 1e12, "fallback_tiles_injected": injected,
+                "fallback_tiles_flagged_last_call": flagged},
         "clocks": clocks,
-        "e2e": {"value": flops_all / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s",
-                "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "host_numa_node": host_node},
+        "e2e": None if args.no_e2e else {
+            "value": flops_all / (ms_e2e / args.steps * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e / args.steps,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "host_numa_node": host_node},
         "gpu_launches": launches,
         "kernel_ms_per_step": {n: round(sum(timer.ms(n)) / args.steps, 3) for n in names if timer.events[n]},
-        "roofline": {"bound": "tensor", "kernel": "attention_kernel<0> (es_sparse_attention)", "achieved": achieved,
-                     "peak": peaks["tflops"], "unit": "TFLOP/s", "frac": achieved / peaks["tflops"],
-                     "peak_source": f"bf16_tflops_sustained of {peaks['source']}", "ms_per_launch": k_ms,
-                     "launches_timed": len(kernel_ms), "traffic": traffic,
-                     "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of one launch captured at the "
-                                       "Wan-1.3B shape (428.1 MB), scaled by tokens x heads (q, k, v read once, out "
-                                       "written once)"},
+        "dense_step_ms_per_branch": round(ms_dense, 3),
+        "roofline": tensor_roofline(
+            "attention_kernel<0> (es_sparse_attention)", achieved, k_ms, len(kernel_ms), clocks, peaks, traffic=traffic,
+            traffic_source="dram__bytes_read.sum + dram__bytes_write.sum of one launch captured at the Wan-1.3B shape "
+                           "(428.1 MB), scaled by tokens x heads (q, k, v read once, out written once)"),
     }
     if world == 1 and not args.no_cpu_baseline:
         tf, sample, dt = cpu_sample(args.workload, args.cpu_seconds, threads)

@@ -121,14 +121,6 @@ int es_reps_metric_static_max_heads(void);
 int es_reps_kmeans(const void* k, const void* v, const void* metric, const void* probes, void* k_rep, void* v_rep,
                    float* log_counts, void* k_mean, void* v_mean, int32_t L, int32_t H, int32_t iters, void* stream);
 
-/* Debugging aid (no counterpart in the reference): with a non-NULL device buffer of es_debug_trace_words() zeroed
- * 32-bit words, the attention kernels launched afterwards write clock stamps of the pipeline stages of their first CTAs
- * into it: [cta < 8][role: 0 softmax thread 0, 1 MMA thread][iteration < 64][half][8 stamps], cycles since CTA start.
- * NULL switches it off. The last 512 words of the buffer are a report area of debug builds: per SM the last stage a CTA
- * reached and the last wait that gave up; with host-mapped memory the host can read them while a kernel is running. */
-int es_debug_set_trace(void* buffer);
-int es_debug_trace_words(void);
-
 #ifdef __cplusplus
 }
 #endif

@@ -5,10 +5,11 @@ There is no fallback: if the library is missing or a call fails, this raises. Py
 pointers; the launch goes on torch's current CUDA stream.
 """
 import ctypes
+import functools
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-# ECHOSPARSE_SM100_LIB selects another build of the same library (for example one compiled with -DES_TRACE).
+# ECHOSPARSE_SM100_LIB selects another build of the same library (for example one compiled with other -D options).
 LIB_PATH = os.environ.get("ECHOSPARSE_SM100_LIB") or os.path.join(_HERE, "_lib", "libechosparse_sm100.so")
 
 _P = ctypes.c_void_p
@@ -64,8 +65,6 @@ SIGNATURES = {
                                _I, _I, _I, _P],
     "es_vsa_tier_rep_bwd": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _P],
     "es_vsa_tier_unpool": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _P],
-    "es_debug_set_trace": [_P],
-    "es_debug_trace_words": [],
 }
 _RESTYPES = {"es_last_error": ctypes.c_char_p, "es_launch_count": ctypes.c_longlong,
              "es_vsa_topk_workspace_bytes": ctypes.c_longlong, "es_vsa_split_plan_workspace_bytes": ctypes.c_longlong,
@@ -112,6 +111,23 @@ def device_status():
 
 def launch_count():
     return int(load().es_launch_count())
+
+
+def device_guard(fn):
+    """Decorator: runs `fn` with the CUDA device of its first tensor argument current, so that the stream looked up by
+    `stream_ptr` and the launch itself follow the tensors and not whatever device the caller's thread had selected
+    (reference: the OptionalCUDAGuard of csrc/vsa/vsa2_api.cpp:64, 80)."""
+    @functools.wraps(fn)
+    def wrapper(*args, **kwargs):
+        import torch
+        for a in args:
+            if isinstance(a, torch.Tensor):
+                if a.is_cuda and a.device.index != torch.cuda.current_device():
+                    with torch.cuda.device(a.device):
+                        return fn(*args, **kwargs)
+                break
+        return fn(*args, **kwargs)
+    return wrapper
 
 
 def ptr(t):

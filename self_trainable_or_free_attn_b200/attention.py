@@ -1,27 +1,41 @@
-"""LSE-guided block-sparse self-attention: the attention processor and its step-to-step state.
+"""LSE-guided block-sparse self-attention on B200: the attention processor and what it keeps between denoising steps.
 
-Same public surface as the reference's `echosparse/attention.py` (`EchoSparseAttention.__init__/__call__/reset`,
-attributes `.backend`, `.K`, `._states`, `._buffers`, `._budget`), same schedule per (CFG branch, layer):
+Public surface of the reference's `echosparse/attention.py` (`EchoSparseAttention.__init__/__call__/reset`, `dense_attention`,
+attributes `.backend`, `.K`, `._states`, `._buffers`, `._plan_scratch`, `._budget`), rebuilt around this backend:
 
-    steps 0 .. dense_steps-2   dense attention; its log2 LSE becomes the stored offset      (attention.py:187-190)
-    step  dense_steps-1        every block through the fixed-offset kernel: exact output, the first
-                               block-probability map and the scales                          (attention.py:215-228)
-    later steps, branch 0      select -> representatives -> fused sparse step -> fallback of flagged tiles ->
-                               estimates for the next selection                              (attention.py:230-248)
-    later steps, branch > 0    branch 0's selection with this branch's own offsets           (attention.py:250-255)
+* What a layer keeps is a PLAN: two bit masks per (tile, head) -- the blocks computed exactly and the blocks the block-mean
+  compensation leaves out -- plus one log2-LSE vector per CFG branch (two buffers that swap roles, so a step never copies
+  its LSE). 12 MB per plan at 75,600 tokens x 40 heads, against 310 MB for the reference's B200 state per (branch, layer).
+  Block lists are expanded from the plan into one workspace shared by all layers (`state="compact"`, the default), or kept
+  expanded per layer to save that expansion (`state="layer"`).
+* The plan of step s + 1 is made at the END of branch 0's call of step s, while the block-probability map is still in the
+  workspace; the map is therefore scratch and never resident. The fused kernel stores the masses of the listed blocks and
+  the estimate kernel those of all others, so the map needs no clearing between steps.
+* One schedule for every state mode, as a small table of phases:
 
-The dense steps use this library's own online-softmax kernel over all blocks instead of FlashAttention-4, so the whole
-path runs on the one native library.
+      DENSE    online-softmax attention over every block; its log2 LSE becomes the branch's offset
+      FULL     every block at the fixed offset: exact output, first map, scales; branch 0 plans the next step
+      SPARSE   plan -> lists, block means, representatives, fused step, recomputation + compensation of flagged tiles;
+               branch 0 also estimates the skipped masses and plans the next step; later branches reuse branch 0's plan
+
+  Steps 0 .. dense_steps-2 are DENSE, step dense_steps-1 is FULL, later steps SPARSE when the branch has run its FULL step
+  and a plan for exactly this step exists, otherwise DENSE again (reference: attention.py:184-200, 272-330).
+* The dense steps run this library's own kernel; nothing depends on FlashAttention.
+* The kernels report a wait that gave up through a status word instead of hanging; `reset()` (once per video) and
+  `check_status()` read it and raise, so a broken launch cannot hand back garbage silently for a whole video.
 """
+import enum
+
 import torch
 
-from . import backends
+from . import _native, backends
 
-BM = 128
-BK = 64
+BM = 128                 # query rows per tile
+BK = 64                  # tokens per kv block
 LOG2E = 1.4426950408889634
 LN2 = 0.6931471805599453
 MIN_BLOCKS = 64          # sequences shorter than 64 kv blocks (4096 tokens) run dense
+NO_SINK = 1 << 30
 
 
 def cdiv(a, b):
@@ -32,9 +46,215 @@ def next_power_of_2(n):
     return 1 << (max(n, 1) - 1).bit_length()
 
 
+def plan_words(nb):
+    """32-bit words of a tile's bit mask: a power of two of bits >= nb, and at least four words per 128 blocks (the fused
+    kernel reads the skip mask four words per block-mean iteration)."""
+    return max(next_power_of_2(nb) // 32, 4 * cdiv(nb, 128))
+
+
+class Phase(enum.Enum):
+    DENSE = 0
+    FULL = 1
+    SPARSE = 2
+
+
+# ------------------------------------------------------------------------------------------------------------ scratch
+class _Buffers:
+    """Scratch of one sequence shape that every call uses: block means, representatives, flags, and the list of all
+    blocks (full step, dense steps)."""
+
+    def __init__(self, L, H, D, device, refine_iters, K):
+        nq, nb = cdiv(L, BM), cdiv(L, BK)
+        self.shape = (L, H, D)
+        self.k_mean = torch.empty(nb, H, D, device=device, dtype=torch.bfloat16)
+        self.v_mean = torch.empty(nb, H, D, device=device, dtype=torch.bfloat16)
+        self.flags = torch.zeros(nq, H, device=device, dtype=torch.int32)
+        self.every_tile = torch.ones(nq, H, device=device, dtype=torch.int32)
+        self.all_counts = torch.full((nq, H), nb, device=device, dtype=torch.int32)
+        self.all_blocks = torch.arange(nb, device=device, dtype=torch.int32).expand(nq, H, nb).contiguous()
+        self.dense_lse = torch.empty(nq * BM, H, device=device)
+        self.reps = K.Representatives(L, H, D, device, iters=refine_iters)
+
+
+class _Lists:
+    """A plan expanded for the kernels: keep mask, ascending block lists with their lengths, refine list."""
+
+    def __init__(self, L, H, device, refine_width):
+        nq, nb = cdiv(L, BM), cdiv(L, BK)
+        self.keep = torch.ones(H, nq, nb, device=device, dtype=torch.uint8)
+        self.counts = torch.zeros(nq, H, device=device, dtype=torch.int32)
+        self.blocks = torch.zeros(nq, H, nb, device=device, dtype=torch.int32)
+        self.refine = torch.full((nq, H, refine_width), nb, device=device, dtype=torch.int32)
+
+
+class _PlanScratch:
+    """Scratch of the sparse path, shared by all layers: the block-probability map and its scales, the lists the current
+    call runs on, the lists the selection writes for the next step, and leftovers of `rebuild_plan` nothing reads."""
+
+    def __init__(self, L, H, device, refine_width):
+        nq, nb = cdiv(L, BM), cdiv(L, BK)
+        self.shape = (L, H, refine_width)
+        self.mass = torch.zeros(H, nq, nb, device=device)
+        self.scale_exact = torch.ones(H, nq, device=device)
+        self.scale_skip = torch.ones(H, nq, device=device)
+        self.lists = _Lists(L, H, device, refine_width)
+        self.next_lists = _Lists(L, H, device, refine_width)
+        self.refine_counts = torch.empty(nq, H, device=device, dtype=torch.int32)
+        self.means = torch.empty(nq, H, nb, device=device, dtype=torch.int32)
+        self.mean_counts = torch.empty(nq, H, device=device, dtype=torch.int32)
+
+    # the names the reference's scratch object has
+    keep = property(lambda self: self.lists.keep)
+    counts = property(lambda self: self.lists.counts)
+    blocks = property(lambda self: self.lists.blocks)
+    refine = property(lambda self: self.lists.refine)
+    next_keep = property(lambda self: self.next_lists.keep)
+
+
+# ------------------------------------------------------------------------------------------------------------ state
+class _Branch:
+    """Offsets of one CFG branch of one layer: two log2-LSE buffers, the kernel reads one and writes the other."""
+
+    def __init__(self, L, H, device):
+        self.buffers = [torch.full((cdiv(L, BM) * BM, H), 1e30, device=device) for _ in range(2)]
+        self.cur = 0
+        self.ready = False           # has run the FULL step of this video
+
+    @property
+    def offset(self):
+        return self.buffers[self.cur]
+
+    @property
+    def next_offset(self):
+        return self.buffers[self.cur ^ 1]
+
+
+class _LayerRecord:
+    """Everything one layer keeps between steps."""
+
+    def __init__(self, L, H, device, keep_lists):
+        self.L, self.H, self.device = L, H, device
+        self.words = plan_words(cdiv(L, BK))
+        self.branches = {}
+        self.plans = []              # [(exact bits, skip bits)], each (H, nq, words) int32
+        self.current = None          # (plan index, step) the branches of this step read
+        self.pending = None          # (plan index, step) branch 0 made for the next step
+        self.keep_lists = keep_lists
+        self.expanded = {}           # plan index -> _Lists (state="layer" only)
+
+    def branch(self, b):
+        if b not in self.branches:
+            self.branches[b] = _Branch(self.L, self.H, self.device)
+        return self.branches[b]
+
+    def plan(self, i):
+        while len(self.plans) <= i:
+            shape = (self.H, cdiv(self.L, BM), self.words)
+            self.plans.append(tuple(torch.full(shape, -1, device=self.device, dtype=torch.int32) for _ in range(2)))
+        return self.plans[i]
+
+    def lists_of(self, i, refine_width):
+        got = self.expanded.get(i)
+        if got is None or got.refine.shape[-1] != refine_width:
+            got = self.expanded[i] = _Lists(self.L, self.H, self.device, refine_width)
+        return got
+
+    # ---- what the reference's compact state exposes
+    @property
+    def offsets(self):
+        return {b: br.offset for b, br in self.branches.items()}
+
+    @property
+    def ready(self):
+        return {b for b, br in self.branches.items() if br.ready}
+
+    def offset(self, branch):
+        return self.branch(branch).offset
+
+
+class _BranchView:
+    """`attn._states[(branch, layer)]`: the tensors the last call of that layer ran on, under the names of the reference's
+    per-(branch, layer) state. Lists, map, scales and flags live in the shared workspace unless the layer keeps its own."""
+
+    def __init__(self, owner, record, branch):
+        self._owner, self._record, self._branch = owner, record, record.branch(branch)
+
+    L = property(lambda self: self._record.L)
+    ready = property(lambda self: self._branch.ready)
+    offset = property(lambda self: self._branch.offset)
+    next_offset = property(lambda self: self._branch.next_offset)
+    offsets = property(lambda self: list(self._branch.buffers))
+    cur = property(lambda self: self._branch.cur)
+    mass = property(lambda self: self._owner._plan_scratch.mass)
+    scale_exact = property(lambda self: self._owner._plan_scratch.scale_exact)
+    scale_skip = property(lambda self: self._owner._plan_scratch.scale_skip)
+    flags = property(lambda self: self._owner._buffers.flags)
+
+    def _used(self):
+        return self._owner._used_lists
+
+    keep = property(lambda self: self._used().keep)
+    keeps = property(lambda self: [self._owner._plan_scratch.lists.keep, self._owner._plan_scratch.next_lists.keep])
+    counts = property(lambda self: self._used().counts)
+    blocks = property(lambda self: self._used().blocks)
+    refine = property(lambda self: self._used().refine)
+
+    @property
+    def skip_bits(self):
+        rec = self._record
+        which = rec.current if rec.current is not None else rec.pending
+        return rec.plan(which[0] if which is not None else 0)[1]
+
+
+class _StateTable:
+    """`attn._states`: layer -> record, and (branch, layer) -> view of one branch. Empty until a layer leaves the dense
+    path; iterating gives the (branch, layer) pairs that exist."""
+
+    def __init__(self, owner):
+        self._owner = owner
+        self._layers = {}
+
+    def record(self, layer):
+        return self._layers.get(layer)
+
+    def put(self, layer, record):
+        self._layers[layer] = record
+
+    def __getitem__(self, key):
+        if isinstance(key, tuple):
+            branch, layer = key
+            rec = self._layers[layer]
+            if branch not in rec.branches:
+                raise KeyError(key)
+            return _BranchView(self._owner, rec, branch)
+        return self._layers[key]
+
+    def __contains__(self, key):
+        if isinstance(key, tuple):
+            return key[1] in self._layers and key[0] in self._layers[key[1]].branches
+        return key in self._layers
+
+    def __iter__(self):
+        return iter(sorted((b, layer) for layer, rec in self._layers.items() for b in rec.branches))
+
+    def __len__(self):
+        return sum(len(rec.branches) for rec in self._layers.values())
+
+    def values(self):
+        return list(self._layers.values())
+
+    def clear(self):
+        self._layers.clear()
+
+
+# ------------------------------------------------------------------------------------------------------------ dense
+def _dense_into(K, q, k, v, buf, out, lse):
+    """Online-softmax attention over every block: the recomputation kernel with every tile flagged."""
+    K.exact_fallback(q, k, v, out, buf.all_counts, buf.all_blocks, lse, buf.every_tile)
+
+
 def dense_attention(q, k, v, return_lse=False, K=None):
-    """Dense softmax attention of [1, L, H, 128] bf16 tensors; with return_lse also the natural-log LSE [1, H, L].
-    Runs the online-softmax kernel over every block (all tiles flagged)."""
+    """Dense softmax attention of [1, L, H, 128] bf16 tensors; with return_lse also the natural-log LSE [1, H, L]."""
     if K is None:
         K = backends.kernels(backends.resolve("auto", q.device))
     B, L, H, D = q.shape
@@ -45,134 +265,40 @@ def dense_attention(q, k, v, return_lse=False, K=None):
         o = torch.nn.functional.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
         return o.transpose(1, 2).contiguous()
     assert B == 1
+    buf = _Buffers.__new__(_Buffers)
     nq, nb = cdiv(L, BM), cdiv(L, BK)
     dev = q.device
-    counts = torch.full((nq, H), nb, device=dev, dtype=torch.int32)
-    blocks = torch.arange(nb, device=dev, dtype=torch.int32).expand(nq, H, nb).contiguous()
-    flags = torch.ones(nq, H, device=dev, dtype=torch.int32)
+    buf.all_counts = torch.full((nq, H), nb, device=dev, dtype=torch.int32)
+    buf.all_blocks = torch.arange(nb, device=dev, dtype=torch.int32).expand(nq, H, nb).contiguous()
+    buf.every_tile = torch.ones(nq, H, device=dev, dtype=torch.int32)
     lse = torch.empty(nq * BM, H, device=dev)
     out = torch.empty_like(q[0])
-    K.exact_fallback(q[0].contiguous(), k[0].contiguous(), v[0].contiguous(), out, counts, blocks, lse, flags)
+    _dense_into(K, q[0].contiguous(), k[0].contiguous(), v[0].contiguous(), buf, out, lse)
     if return_lse:
         return out[None], (lse[:L].t() * LN2)[None]
     return out[None]
 
 
-class _LayerState:
-    """State of one (branch, layer) (reference: attention.py:38-69)."""
-
-    def __init__(self, L, H, device):
-        nq, nb = cdiv(L, BM), cdiv(L, BK)
-        self.L = L
-        self.offsets = [torch.full((nq * BM, H), 1e30, device=device) for _ in range(2)]
-        self.cur = 0
-        self.mass = torch.zeros(H, nq, nb, device=device)
-        self.keeps = [torch.ones(H, nq, nb, device=device, dtype=torch.uint8) for _ in range(2)]
-        self.kc = 0
-        self.scale_exact = torch.ones(H, nq, device=device)
-        self.scale_skip = torch.ones(H, nq, device=device)
-        self.counts = torch.empty(nq, H, device=device, dtype=torch.int32)
-        self.blocks = torch.zeros(nq, H, nb, device=device, dtype=torch.int32)
-        self.flags = torch.zeros(nq, H, device=device, dtype=torch.int32)
-        words = max(next_power_of_2(nb) // 32, 4 * cdiv(nb, 128))
-        self.skip_bits = torch.full((H, nq, words), -1, device=device, dtype=torch.int32)
-        self.refine = torch.empty(nq, H, 0, device=device, dtype=torch.int32)
-        self.ready = False
-
-    @property
-    def offset(self):
-        return self.offsets[self.cur]
-
-    @property
-    def next_offset(self):
-        return self.offsets[1 - self.cur]
-
-    @property
-    def keep(self):
-        return self.keeps[self.kc]
-
-
-class _CompactState:
-    """Compact state of one layer (reference: attention.py:72-97): the offsets of every branch and the plans, each a pair
-    of bit masks (exact blocks, blocks skipped by the block-mean compensation), 2 x H x nq x words x 4 bytes: 12 MB per
-    plan at 75,600 tokens and 40 heads against the 310 MB of a `_LayerState`. Branch 0 writes the other of two plans for
-    the next step while later branches still read the current one."""
-
-    def __init__(self, L, H, device):
-        nb = cdiv(L, BK)
-        self.L, self.H, self.device = L, H, device
-        self.words = max(next_power_of_2(nb) // 32, 4 * cdiv(nb, 128))
-        self.plans = []
-        self.offsets = {}
-        self.ready = set()          # branches that have run the full step
-        self.current = None         # (plan, step) used by the branches of this step
-        self.pending = None         # (plan, step) made by branch 0 for the next step
-
-    def plan(self, i):
-        while len(self.plans) <= i:
-            shape = (self.H, cdiv(self.L, BM), self.words)
-            self.plans.append(tuple(torch.full(shape, -1, device=self.device, dtype=torch.int32) for _ in range(2)))
-        return self.plans[i]
-
-    def offset(self, branch):
-        if branch not in self.offsets:
-            self.offsets[branch] = torch.full((cdiv(self.L, BM) * BM, self.H), 1e30, device=self.device)
-        return self.offsets[branch]
-
-
-class _PlanScratch:
-    """Per-call tensors of the compact path, shared by all layers (reference: attention.py:99-117)."""
-
-    def __init__(self, L, H, device, refine_width):
-        nq, nb = cdiv(L, BM), cdiv(L, BK)
-        self.shape = (L, H, refine_width)
-        self.mass = torch.empty(H, nq, nb, device=device)
-        self.keep = torch.empty(H, nq, nb, device=device, dtype=torch.uint8)
-        self.next_keep = torch.empty(H, nq, nb, device=device, dtype=torch.uint8)
-        self.scale_exact = torch.empty(H, nq, device=device)
-        self.scale_skip = torch.empty(H, nq, device=device)
-        self.counts = torch.empty(nq, H, device=device, dtype=torch.int32)
-        self.blocks = torch.zeros(nq, H, nb, device=device, dtype=torch.int32)
-        self.refine = torch.empty(nq, H, refine_width, device=device, dtype=torch.int32)
-        self.refine_counts = torch.empty(nq, H, device=device, dtype=torch.int32)
-        self.means = torch.empty(nq, H, nb, device=device, dtype=torch.int32)
-        self.mean_counts = torch.empty(nq, H, device=device, dtype=torch.int32)
-        self.next_offset = torch.empty(nq * BM, H, device=device)
-
-
-class _Buffers:
-    """Per-call scratch for one sequence shape (reference: attention.py:119-130)."""
-
-    def __init__(self, L, H, D, device, refine_iters, K):
-        nq, nb = cdiv(L, BM), cdiv(L, BK)
-        self.shape = (L, H, D)
-        self.k_mean = torch.empty(nb, H, D, device=device, dtype=torch.bfloat16)
-        self.v_mean = torch.empty(nb, H, D, device=device, dtype=torch.bfloat16)
-        self.flags = torch.empty(nq, H, device=device, dtype=torch.int32)
-        self.all_counts = torch.full((nq, H), nb, device=device, dtype=torch.int32)
-        self.all_blocks = torch.arange(nb, device=device, dtype=torch.int32).expand(nq, H, nb).contiguous()
-        self.reps = K.Representatives(L, H, D, device, iters=refine_iters)
-
-
+# ------------------------------------------------------------------------------------------------------------ processor
 class EchoSparseAttention:
     """Self-attention for one video at a time; call `reset()` before each video.
 
-    `__call__(q, k, v, step, branch, layer)` takes [1, L, H, 128] bf16 tensors. `branch` numbers the transformer
-    forwards of a denoising step (0: conditional, 1: unconditional); later branches reuse branch 0's block
-    selection of the same step and layer. `sink`: first kv block that every query tile computes exactly (text or
-    other conditioning tokens placed after the video tokens). `rows` is accepted for signature compatibility.
+    `__call__(q, k, v, step, branch, layer)` takes [1, L, H, 128] bf16 tensors. `branch` numbers the transformer forwards
+    of a denoising step (0: conditional, 1: unconditional); later branches reuse branch 0's block selection of the same
+    step and layer. `sink`: first kv block that every query tile computes exactly (text or other conditioning tokens placed
+    after the video tokens). `rows` is accepted for signature compatibility (every tile is computed).
 
     `gpu`: "auto" or "b200". `min_blocks`: sequences with fewer kv blocks run dense (the reference's constant 64).
-    `state`: "layer" keeps the reference's B200 state per (branch, layer) (mass map, keep masks, lists); "compact" keeps
-    only the offsets and the bit-mask plans per layer (the reference's state on its other GPUs, attention.py:272-330) and
-    rebuilds the lists from the plan every step: 25 x less resident state for two more small kernels per call.
+    `state`: "compact" keeps per layer the offsets and the bit-mask plans and expands a plan into the shared workspace at
+    every call; "layer" also keeps the expanded lists per layer.
     """
 
     def __init__(self, density=0.10, dense_steps=10, dense_layers=(0,), refine_iters=6, threshold=60.0, gpu="auto",
-                 min_blocks=MIN_BLOCKS, state="layer"):
-        assert state in ("layer", "compact"), "state must be 'layer' or 'compact'"
-        self.state = state
+                 min_blocks=MIN_BLOCKS, state="compact"):
+        if state not in ("layer", "compact"):
+            raise ValueError("state must be 'layer' or 'compact'")
         assert dense_steps >= 2, "the first sparse step needs the LSE of a dense step and a full-block step"
+        self.state = state
         self.density = density
         self.dense_steps = dense_steps
         self.dense_layers = set(dense_layers)
@@ -182,181 +308,162 @@ class EchoSparseAttention:
         backends.check_name(gpu)
         self.gpu = gpu
         self.backend = None             # resolved from the device of the first call
-        self._device = None
         self.K = None
-        self._states = {}
+        self._device = None
+        self._states = _StateTable(self)
         self._buffers = None
         self._plan_scratch = None
+        self._used_lists = None         # the lists the last sparse / full call ran on
 
+    # ---- housekeeping
     def reset(self):
-        for st in self._states.values():
-            if isinstance(st, _CompactState):
-                st.ready.clear()
-                st.current = st.pending = None
-            else:
-                st.ready = False
+        """Forget the previous video: every branch has to run its dense and full steps again. Also the place where the
+        kernels' status word is read (one device synchronisation per video)."""
+        for rec in self._states.values():
+            for br in rec.branches.values():
+                br.ready = False
+            rec.current = rec.pending = None
+        self.check_status()
 
-    def __call__(self, q, k, v, step, branch, layer, sink=None, rows=None):
-        B, L, H, D = q.shape
-        assert B == 1, "batch size 1 only"
-        if q.device != self._device:
-            self.backend = backends.resolve(self.gpu, q.device)
-            self.K = backends.kernels(self.backend)
-            self._states.clear()
-            self._buffers = self._plan_scratch = None
-            self._device = q.device
-        if layer in self.dense_layers or cdiv(L, BK) < self.min_blocks:
-            return dense_attention(q, k, v, K=self.K)
-        if self.state == "compact":
-            return self._call_compact(q, k, v, step, branch, layer, sink)
-        return self._call_b200(q, k, v, step, branch, layer, sink)
+    def check_status(self):
+        """Raises NativeError if a kernel's bounded wait gave up since the last check (the word is cleared). Synchronises
+        the device, so call it where that is cheap: between videos, or once per denoising step."""
+        if self._device is None:
+            return
+        with torch.cuda.device(self._device):
+            code = _native.device_status()
+        if code != 0:
+            raise _native.NativeError(f"an attention kernel gave up a wait (status {code}: wait {code % 1000} in CTA "
+                                      f"{code // 1000}); the outputs since the last check are not valid")
 
-    def _call_compact(self, q, k, v, step, branch, layer, sink):
-        """The schedule of `_call_b200` on the compact state (reference: attention.py:272-330): a step reads its plan,
-        rebuilds the lists, runs the fused kernels and, in branch 0, selects and packs the plan of the next step."""
-        L, H, D = q[0].shape
-        st = self._states.get(layer)
-        if st is None or st.L != L:
-            self._states[layer] = None
-            st = self._states[layer] = _CompactState(L, H, q.device)
-        offset = st.offset(branch)
-        if branch == 0 and step >= self.dense_steps:
-            st.current = st.pending if st.pending is not None and st.pending[1] == step else None
-            st.pending = None
-        full = step == self.dense_steps - 1
-        sparse = step >= self.dense_steps and branch in st.ready and st.current is not None and st.current[1] == step
-        if not (full or sparse):
-            out, lse = dense_attention(q, k, v, return_lse=True, K=self.K)
-            offset[:L].copy_(lse[0].t() * LOG2E)
-            return out
-        K = self.K
-        q, k, v = q[0].contiguous(), k[0].contiguous(), v[0].contiguous()
-        top, refined = self._budget(cdiv(L, BK))
-        width = -(-refined // 32) * 32
-        buf = self._scratch(L, H, D, q.device)
-        ps = self._plan_scratch
-        if ps is None or ps.shape != (L, H, width):
-            self._plan_scratch = None
-            ps = self._plan_scratch = _PlanScratch(L, H, q.device, width)
-        out = torch.empty_like(q)
-        if full:
-            ps.keep.fill_(1)
-            ps.mass.zero_()
-            K.block_attention(q, k, v, out, buf.all_counts, buf.all_blocks, offset, ps.next_offset, buf.flags,
-                              mass=ps.mass, threshold=self.threshold)
-            K.exact_fallback(q, k, v, out, buf.all_counts, buf.all_blocks, ps.next_offset, buf.flags)
-            K.full_step_scales(offset, ps.next_offset, ps.scale_exact, ps.scale_skip, L)
-            st.ready.add(branch)
-        else:
-            exact, skip = st.plan(st.current[0])
-            K.rebuild_plan(exact, skip, ps.keep, ps.counts, ps.blocks, ps.refine, ps.refine_counts, ps.means,
-                           ps.mean_counts)
-            K.block_means(k, v, buf.k_mean, buf.v_mean)
-            buf.reps.build(q, k, v)
-            if branch == 0:
-                ps.mass.zero_()
-            K.sparse_attention(q, k, v, buf.k_mean, buf.v_mean, skip, out, ps.counts, ps.blocks, offset, ps.next_offset,
-                               buf.flags, ps.refine, buf.reps.k, buf.reps.v, buf.reps.log_counts,
-                               mass=ps.mass if branch == 0 else None, threshold=self.threshold)
-            K.exact_fallback(q, k, v, out, ps.counts, ps.blocks, ps.next_offset, buf.flags)
-            K.compensate_fallback(q, buf.k_mean, buf.v_mean, ps.keep, ps.next_offset, out, buf.flags)
-            if branch == 0:
-                K.estimate_skipped(q, buf.k_mean, ps.keep, offset, ps.next_offset, ps.mass, ps.scale_exact, ps.scale_skip)
-        if branch == 0:
-            # the next step's plan, after this step's last use of the current one in a single branch
-            plan = 0 if st.current is None else st.current[0] ^ (len(st.offsets) > 1)
-            exact, skip = st.plan(plan)
-            K.select_blocks(ps.mass, ps.keep, ps.scale_exact, ps.scale_skip, ps.next_keep, ps.counts, ps.blocks, buf.flags,
-                            skip, ps.refine, top, refined, L, sink=1 << 30 if sink is None else sink)
-            K.pack_plan(ps.next_keep, exact)
-            st.pending = (plan, step + 1)
-        offset.copy_(ps.next_offset)
-        return out[None]
-
-    def _call_b200(self, q, k, v, step, branch, layer, sink):
-        L, H, D = q[0].shape
-        st = self._state(branch, layer, L, H, q.device)
-        if step < self.dense_steps - 1 or (step >= self.dense_steps and not st.ready):
-            out, lse = dense_attention(q, k, v, return_lse=True, K=self.K)
-            st.offset[:L].copy_(lse[0].t() * LOG2E)
-            return out
-        q, k, v = q[0].contiguous(), k[0].contiguous(), v[0].contiguous()
-        buf = self._scratch(L, H, D, q.device)
-        if step < self.dense_steps:
-            out = self._full_step(q, k, v, st, buf)
-        elif branch == 0:
-            out = self._sparse_step(q, k, v, st, buf, sink)
-        else:
-            out = self._shared_step(q, k, v, st, self._states[(0, layer)], buf)
-        st.cur ^= 1
-        return out[None]
-
-    def _state(self, branch, layer, L, H, device):
-        st = self._states.get((branch, layer))
-        if st is None or st.L != L:
-            self._states[(branch, layer)] = None          # free the old buffers before allocating new ones
-            st = self._states[(branch, layer)] = _LayerState(L, H, device)
-        return st
-
-    def _scratch(self, L, H, D, device):
-        if self._buffers is None or self._buffers.shape != (L, H, D):
-            self._buffers = None                           # one sequence shape at a time
-            self._buffers = _Buffers(L, H, D, device, self.refine_iters, self.K)
-        return self._buffers
-
-    def _full_step(self, q, k, v, st, buf):
-        """Every block at the fixed offset: exact output and the first block-probability map."""
-        K = self.K
-        out = torch.empty_like(q)
-        st.kc ^= 1
-        st.keep.fill_(1)
-        st.mass.zero_()
-        K.block_attention(q, k, v, out, buf.all_counts, buf.all_blocks, st.offset, st.next_offset, buf.flags,
-                          mass=st.mass, threshold=self.threshold)
-        K.exact_fallback(q, k, v, out, buf.all_counts, buf.all_blocks, st.next_offset, buf.flags)
-        K.full_step_scales(st.offset, st.next_offset, st.scale_exact, st.scale_skip, st.L)
-        st.flags.copy_(buf.flags)
-        st.ready = True
-        return out
-
-    def _sparse_step(self, q, k, v, st, buf, sink):
-        K = self.K
-        L, H, _ = q.shape
-        nq, nb = cdiv(L, BM), cdiv(L, BK)
-        K.block_means(k, v, buf.k_mean, buf.v_mean)
-        top, refined = self._budget(nb)
-        width = -(-refined // 32) * 32
-        if st.refine.shape[-1] != width:
-            st.refine = torch.empty(nq, H, width, device=q.device, dtype=torch.int32)
-        keep_prev = st.keep
-        st.kc ^= 1
-        K.select_blocks(st.mass, keep_prev, st.scale_exact, st.scale_skip, st.keep, st.counts, st.blocks, st.flags,
-                        st.skip_bits, st.refine, top, refined, L, sink=1 << 30 if sink is None else sink)
-        st.mass.zero_()
-        out = torch.empty_like(q)
-        self._attend(q, k, v, st, st, buf, out, mass=st.mass)
-        st.flags.copy_(buf.flags)
-        K.estimate_skipped(q, buf.k_mean, st.keep, st.offset, st.next_offset, st.mass, st.scale_exact, st.scale_skip)
-        return out
-
-    def _shared_step(self, q, k, v, st, sel, buf):
-        """A later CFG branch: branch 0's block selection, this branch's own offsets."""
-        self.K.block_means(k, v, buf.k_mean, buf.v_mean)
-        out = torch.empty_like(q)
-        self._attend(q, k, v, st, sel, buf, out)
-        return out
-
-    def _attend(self, q, k, v, st, sel, buf, out, mass=None):
-        K, reps = self.K, buf.reps
-        reps.build(q, k, v)
-        K.sparse_attention(q, k, v, buf.k_mean, buf.v_mean, sel.skip_bits, out, sel.counts, sel.blocks, st.offset,
-                           st.next_offset, buf.flags, sel.refine, reps.k, reps.v, reps.log_counts, mass=mass,
-                           threshold=self.threshold)
-        # tiles whose offset was too far off: online softmax over the same list, then block-mean compensation
-        K.exact_fallback(q, k, v, out, sel.counts, sel.blocks, st.next_offset, buf.flags)
-        K.compensate_fallback(q, buf.k_mean, buf.v_mean, sel.keep, st.next_offset, out, buf.flags)
+    def _bind(self, device):
+        self.backend = backends.resolve(self.gpu, device)
+        self.K = backends.kernels(self.backend)
+        self._states.clear()
+        self._buffers = self._plan_scratch = self._used_lists = None
+        self._device = device
 
     def _budget(self, nb):
         """Exactly computed blocks per tile, and refined blocks (four representatives each) per tile."""
         top = max(1, int(round(self.density * nb)))
         return top, max(0, int(round((nb - top) / 3)))
+
+    def _scratch(self, L, H, D, device):
+        if self._buffers is None or self._buffers.shape != (L, H, D):
+            self._buffers = self._plan_scratch = self._used_lists = None       # one sequence shape at a time
+            self._buffers = _Buffers(L, H, D, device, self.refine_iters, self.K)
+        return self._buffers
+
+    def _sparse_scratch(self, L, H, device, refine_width):
+        ps = self._plan_scratch
+        if ps is None or ps.shape != (L, H, refine_width):
+            self._plan_scratch = self._used_lists = None
+            ps = self._plan_scratch = _PlanScratch(L, H, device, refine_width)
+        return ps
+
+    def _record(self, layer, L, H, device):
+        rec = self._states.record(layer)
+        if rec is None or rec.L != L or rec.H != H:
+            self._states.put(layer, None)                    # let the old buffers go before the new ones are made
+            rec = _LayerRecord(L, H, device, keep_lists=self.state == "layer")
+            self._states.put(layer, rec)
+        return rec
+
+    # ---- the schedule
+    def _phase(self, rec, br, step, branch):
+        if branch == 0 and step >= self.dense_steps:
+            # the plan branch 0 made at the end of the previous step becomes this step's, if it was made for this step
+            rec.current = rec.pending if rec.pending is not None and rec.pending[1] == step else None
+            rec.pending = None
+        if step == self.dense_steps - 1:
+            return Phase.FULL
+        if step >= self.dense_steps and br.ready and rec.current is not None and rec.current[1] == step:
+            return Phase.SPARSE
+        return Phase.DENSE
+
+    def __call__(self, q, k, v, step, branch, layer, sink=None, rows=None):
+        B, L, H, D = q.shape
+        assert B == 1, "batch size 1 only"
+        if q.device != self._device:
+            self._bind(q.device)
+        if cdiv(L, BK) < self.min_blocks:
+            return dense_attention(q, k, v, K=self.K)
+        if layer in self.dense_layers:
+            # a full-length layer that always runs dense: the workspace already holds the list of all blocks
+            buf = self._scratch(L, H, D, q.device)
+            out = torch.empty_like(q[0])
+            _dense_into(self.K, q[0].contiguous(), k[0].contiguous(), v[0].contiguous(), buf, out, buf.dense_lse)
+            return out[None]
+        with torch.cuda.device(q.device):
+            return self._step(q[0].contiguous(), k[0].contiguous(), v[0].contiguous(), step, branch, layer,
+                              NO_SINK if sink is None else sink)[None]
+
+    def _step(self, q, k, v, step, branch, layer, sink):
+        L, H, D = q.shape
+        K = self.K
+        rec = self._record(layer, L, H, q.device)
+        br = rec.branch(branch)
+        buf = self._scratch(L, H, D, q.device)
+        phase = self._phase(rec, br, step, branch)
+        out = torch.empty_like(q)
+        if phase is Phase.DENSE:
+            _dense_into(K, q, k, v, buf, out, br.offset)
+            return out
+        top, refined = self._budget(cdiv(L, BK))
+        ps = self._sparse_scratch(L, H, q.device, cdiv(refined, 32) * 32)
+        if phase is Phase.FULL:
+            lists = None
+            ps.lists.keep.fill_(1)                           # "kept before": every block, for the first selection
+            kept = ps.lists.keep
+            K.block_attention(q, k, v, out, buf.all_counts, buf.all_blocks, br.offset, br.next_offset, buf.flags,
+                              mass=ps.mass if branch == 0 else None, threshold=self.threshold)
+            K.exact_fallback(q, k, v, out, buf.all_counts, buf.all_blocks, br.next_offset, buf.flags)
+            if branch == 0:
+                K.full_step_scales(br.offset, br.next_offset, ps.scale_exact, ps.scale_skip, L)
+            br.ready = True
+        else:
+            exact, skip = rec.plan(rec.current[0])
+            lists = self._expand(rec, rec.current[0], exact, skip, ps)
+            kept = lists.keep
+            K.block_means(k, v, buf.k_mean, buf.v_mean)
+            buf.reps.build(q, k, v)
+            K.sparse_attention(q, k, v, buf.k_mean, buf.v_mean, skip, out, lists.counts, lists.blocks, br.offset,
+                               br.next_offset, buf.flags, lists.refine, buf.reps.k, buf.reps.v, buf.reps.log_counts,
+                               mass=ps.mass if branch == 0 else None, threshold=self.threshold)
+            # tiles whose offset was too far off: online softmax over the same list, then block-mean compensation
+            K.exact_fallback(q, k, v, out, lists.counts, lists.blocks, br.next_offset, buf.flags)
+            K.compensate_fallback(q, buf.k_mean, buf.v_mean, lists.keep, br.next_offset, out, buf.flags)
+            if branch == 0:
+                K.estimate_skipped(q, buf.k_mean, lists.keep, br.offset, br.next_offset, ps.mass, ps.scale_exact,
+                                   ps.scale_skip)
+        if lists is not None:
+            self._used_lists = lists
+        elif self._used_lists is None:
+            self._used_lists = ps.lists
+        if branch == 0:
+            self._plan_next(rec, ps, kept, buf.flags, top, refined, L, sink, step)
+        br.cur ^= 1
+        return out
+
+    def _expand(self, rec, index, exact, skip, ps):
+        """The lists of plan `index`: the layer's own copy (state="layer", filled when the plan was made) or the shared
+        workspace, expanded from the two bit masks now."""
+        if rec.keep_lists and index in rec.expanded and rec.expanded[index].refine.shape[-1] == ps.shape[2]:
+            return rec.expanded[index]
+        dst = ps.lists
+        self.K.rebuild_plan(exact, skip, dst.keep, dst.counts, dst.blocks, dst.refine, ps.refine_counts, ps.means,
+                            ps.mean_counts)
+        return dst
+
+    def _plan_next(self, rec, ps, kept, flags, top, refined, L, sink, step):
+        """Branch 0, end of a step: select the next step's blocks from the map in the workspace and pack them as a plan.
+        With several branches the other of two plans is written, because later branches of this step still read the
+        current one; a single branch rewrites its plan in place (unless the layer keeps expanded lists: the selection
+        reads the current keep mask while it writes the next one, so those always alternate)."""
+        index = 0 if rec.current is None else rec.current[0] ^ (len(rec.branches) > 1 or rec.keep_lists)
+        exact, skip = rec.plan(index)
+        dst = rec.lists_of(index, ps.shape[2]) if rec.keep_lists else ps.next_lists
+        self.K.select_blocks(ps.mass, kept, ps.scale_exact, ps.scale_skip, dst.keep, dst.counts, dst.blocks, flags, skip,
+                             dst.refine, top, refined, L, sink=sink)
+        self.K.pack_plan(dst.keep, exact)
+        rec.pending = (index, step + 1)

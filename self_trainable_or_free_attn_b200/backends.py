@@ -1,5 +1,5 @@
 """The one GPU backend: B200 (sm_100a), hand-written CUDA. Replaces the reference's multi-generation dispatch
-(echosparse/backends.py:15-61): same function names, but anything that is not compute capability 10.x raises; there is
+(echosparse/backends.py:15-61): same function names, but anything that is not compute capability 10.0 raises; there is
 no Triton path and no CPU fallback.
 """
 import importlib
@@ -18,14 +18,15 @@ def check_name(gpu):
 
 
 def resolve(gpu, device):
-    """Backend name for `gpu` ("auto" or "b200") on `device`; raises if the device is not a compute-10.x CUDA GPU."""
+    """Backend name for `gpu` ("auto" or "b200") on `device`; raises if the device is not a compute-10.0 CUDA GPU."""
     check_name(gpu)
     device = torch.device(device)
     if device.type != "cuda":
         raise ValueError(f"EchoSparse runs on CUDA tensors; got a tensor on {device}")
     major, minor = torch.cuda.get_device_capability(device)
-    if major != 10:
-        raise RuntimeError(f"{device} has compute capability {major}.{minor}; this build needs a B200 (10.x)")
+    if (major, minor) != (10, 0):
+        # the library is compiled for sm_100a only: architecture-specific code, not forward compatible within 10.x
+        raise RuntimeError(f"{device} has compute capability {major}.{minor}; this build needs a B200 (10.0)")
     return "b200"
 
 

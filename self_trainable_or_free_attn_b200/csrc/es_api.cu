@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <cstring>
 #include <mutex>
+#include <vector>
 
 namespace es {
 
@@ -32,6 +33,24 @@ int* device_status_ptr() {
         ptrs[dev] = static_cast<int*>(p);
     }
     return ptrs[dev];
+}
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a property of (kernel, device): a process that uses several GPUs has
+// to opt in on each of them. The pairs already done are remembered, so a launch costs one short list walk.
+int opt_in_shared_memory(const void* kernel, int bytes) {
+    struct Done { int dev; const void* kernel; int bytes; };
+    static std::mutex mu;
+    static std::vector<Done> done;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
+    std::lock_guard<std::mutex> lock(mu);
+    for (const Done& d : done)
+        if (d.dev == dev && d.kernel == kernel && d.bytes >= bytes) return 0;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
+    done.push_back({dev, kernel, bytes});
+    return 0;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -15,6 +15,9 @@ int* device_status_ptr();
 // One more kernel launched by this library (read with es_launch_count).
 void count_launch();
 
+// Lets `kernel` use `bytes` of dynamic shared memory on the current device (once per device and kernel). 0 or an error code.
+int opt_in_shared_memory(const void* kernel, int bytes);
+
 int encode_tensor_map(CUtensorMap* m, CUtensorMapDataType dt, uint32_t rank, void* base, const cuuint64_t* dims,
                       const cuuint64_t* strides_bytes, const cuuint32_t* box, const cuuint32_t* elem_strides,
                       CUtensorMapSwizzle swizzle);

@@ -16,15 +16,16 @@
 //
 // Pipeline. An iteration covers 128 columns (two 64-token blocks, 128 block means, or 32 refine entries x 4).
 //   warps 0-7  softmax: warp w owns rows 32 (w % 4) .. +31 of the tile and columns 64 (w / 4) .. +63 of the iteration
-//   warp 8     issues the tcgen05 MMAs (one elected lane); warps 9 and 10 issue the TMA loads / cp.async gathers of the K
-//              and of the V tiles (control code is one dependent chain per tile: two warps halve its length)
+//   warp 8     issues the tcgen05 MMAs (one elected lane); warps 9 and 10 issue the TMA loads of the K and of the V
+//              tiles (control code is one dependent chain per tile: two warps halve its length); warp 11 sums and
+//              stores the block masses
 // Tensor memory (512 columns): S of even iterations [0,128), S of odd iterations [128,256), O [256,384), Q [384,448).
 // Q sits in tensor memory as the A operand of QK^T, so the only shared-memory traffic of the MMAs is K and V: with Q in
 // shared memory a 128 x 64 x 16 MMA reads 6 KB in the 32 clocks it computes, more than the 128 B/clock an SM delivers.
 // P (bf16 pairs) is written over the S columns it came from and is the A operand of PV. Two S buffers let QK of
 // iteration i + 1 run while the softmax warps work on iteration i; PV(i) and QK(i + 2) follow as soon as P(i) is stored.
-// K and V tiles (32 KB each, [d half][128 rows][128 B], four 8 KB TMA boxes) travel through a ring of 7 shared-memory slots,
-// about three iterations ahead of the MMAs.
+// K and V tiles (32 KB each, [d half][128 rows][128 B], four 8 KB TMA boxes; representative rows: 64 boxes of 512 B)
+// travel through a ring of NSLOT shared-memory slots, about three iterations ahead of the MMAs.
 #include "es_ptx.cuh"
 #include "es_api_internal.h"
 
@@ -92,20 +93,7 @@ struct AttnArgs {
     float tail_log2;             // log2(tail_valid)
     int nvirt, nref;             // mean iterations (128 blocks each), refine iterations (32 list entries each)
     int* status;
-    uint32_t* trace;             // optional clock trace of the first CTAs (null: off); see es_debug_set_trace
 };
-
-// Clock trace for pipeline debugging: CTAs 0 .. TRACE_CTAS-1, softmax thread 0 (role 0) and the MMA warp (role 1),
-// the first TRACE_ITERS iterations, 8 time stamps each (clock cycles since the CTA started).
-constexpr int TRACE_CTAS = 8, TRACE_ITERS = 64;
-#ifdef ES_TRACE
-__device__ __forceinline__ void trace_put(uint32_t* tr, int role, int i, int k, long long t0) {
-    if (tr != nullptr && blockIdx.x < TRACE_CTAS && i < TRACE_ITERS)
-        tr[(((size_t)blockIdx.x * 2 + role) * TRACE_ITERS + i) * 8 + k] = (uint32_t)(clock64() - t0);
-}
-#else
-__device__ __forceinline__ void trace_put(uint32_t*, int, int, int, long long) {}    // compiled out of release builds
-#endif
 
 // p = 2^x for a pair of columns. MUFU computes 16 exponentials per clock and SM, about as many clocks as the tensor
 // cores need for the same tile, so a share of the pairs can be computed on the FMA pipe instead: x = n + f with
@@ -176,7 +164,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     constexpr bool FALLBACK = MODE == 1;       // online-softmax recomputation of flagged tiles
     constexpr bool COMPENSATE = MODE == 2;     // block-mean compensation of flagged tiles, added to out / lse in place
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const long long t_start = clock64();
     // adjacent CTAs are adjacent query tiles of one head: their kv lists overlap in L2
     const int qb = blockIdx.x % a.nq, h = blockIdx.x / a.nq;
     const int th_idx = qb * a.H + h;
@@ -201,7 +188,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     // a wait has given up earlier (the status word is set until the host reads it): do not start more work
     if (*reinterpret_cast<volatile int*>(a.status) != 0) return;
 
-    if (tid == 0) dbg_stage(1);
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     Ctl* ctl = reinterpret_cast<Ctl*>(smem_raw + SMEM_CTL);
@@ -242,7 +228,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = ctl->tmem_base;
-    if (tid == 0) dbg_stage(2);
 
     const int n64 = n64_early;
     const int n = (n64 + 1) >> 1;                     // exact iterations: pairs of 64-token blocks
@@ -298,11 +283,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
             ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;     // the other lanes sleep at the shuffle instead of polling
             if (!ok) return;
             const uint32_t dst = sRing + slot * TILE_BYTES, bar = full0 + 8 * slot;
-#ifdef ES_EXPERIMENT_NOLOAD
-            if (seq >= NSLOT) {                 // timing experiment only: tiles after the first ring round are not loaded
-                if (lane == 0) mbar_arrive(bar);
-            } else
-#endif
             if (kind != 2) {
                 if (lane == 0) mbar_arrive_expect_tx(bar, TILE_BYTES);
                 __syncwarp();
@@ -373,9 +353,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         };
         // S[buf] <- Q K^T. The S columns also hold the previous P of that buffer: every earlier use must have been handed
         // back by the softmax warps (pfull) before they are overwritten; the PV that read it was issued before (in order).
-        auto issue_qk = [&](int buf, int ti = TRACE_ITERS) {
+        auto issue_qk = [&](int buf) {
             const uint32_t slot = take();
-            if (lane == 0) trace_put(a.trace, 1, ti, 5, t_start);
             while (ok && wP[buf] < nQK[buf]) {
                 ok = mbar_wait_warp(pfull0 + 8 * buf, wP[buf] & 1, abort_flag, a.status, 203);
                 ++wP[buf];
@@ -402,11 +381,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
         if (nt > 1) issue_qk(1);
         for (int i = 0; i < nt && ok; ++i) {
             const int buf = i & 1;
-            if (lane == 0) trace_put(a.trace, 1, i, 0, t_start);
             const uint32_t slot = take();
-            if (lane == 0) trace_put(a.trace, 1, i, 1, t_start);
             ok = ok && mbar_wait_warp(pfull0 + 8 * buf, wP[buf] & 1, abort_flag, a.status, 205);   // P(i) stored
-            if (lane == 0) trace_put(a.trace, 1, i, 2, t_start);
             if (!ok) break;
             ++wP[buf];
             tc_fence_after();
@@ -422,9 +398,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 if (i + 1 == nt) umma_commit(smem_u32(&ctl->ofull));
             }
             __syncwarp();
-            if (lane == 0) trace_put(a.trace, 1, i, 3, t_start);
-            if (i + 2 < nt) issue_qk(buf, i);
-            if (lane == 0) trace_put(a.trace, 1, i, 4, t_start);
+            if (i + 2 < nt) issue_qk(buf);
         }
         // every MMA issued above has finished before tensor memory is freed
         if (elect_one()) umma_commit(smem_u32(&ctl->drain));
@@ -542,17 +516,14 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 w0 = (uint32_t)__ldg(bits + 4 * cur_idx + 2 * ch);
                 w1 = (uint32_t)__ldg(bits + 4 * cur_idx + 2 * ch + 1);
             }
-            if (tid == 0) trace_put(a.trace, 0, i, 0, t_start);
             ok = ok && mbar_wait_warp(smem_u32(&ctl->sfull[buf]), uS[buf] & 1, abort_flag, a.status, 302);
             if (!ok) break;
-            if (tid == 0) trace_put(a.trace, 0, i, 1, t_start);
             ++uS[buf];
             tc_fence_after();
             const uint32_t scol = lane_base + buf * 128 + 64 * ch;
             tmem_ld32(scol, &s[0]);
             tmem_ld32(scol + 32, &s[32]);
             tmem_wait_ld();
-            if (tid == 0) trace_put(a.trace, 0, i, 2, t_start);
             float2 acc = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
             uint32_t pk[32];
             if (exact) {
@@ -627,12 +598,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                     pk[c / 2 + 1] = pack_bf16x2(p1.x, p1.y);
                 }
             }
-            if (tid == 0) trace_put(a.trace, 0, i, 3, t_start);
             tmem_st32(scol, pk);                       // P over the first 32 of this thread's own 64 S columns
             tmem_wait_st();
             tc_fence_before();
             mbar_arrive(smem_u32(&ctl->pfull[buf]));
-            if (tid == 0) trace_put(a.trace, 0, i, 4, t_start);
             acc = __fadd2_rn(acc, acc1);
             lsum = __fadd2_rn(lsum, acc);
             if (want_mass && exact) {
@@ -648,7 +617,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
                 __syncwarp();
                 if (lane == 0) mbar_arrive(smem_u32(&ctl->massbar[set]));
             }
-            if (tid == 0) trace_put(a.trace, 0, i, 5, t_start);
             kind = nkind; idx = nidx; blk = nblk;
         }
 
@@ -713,7 +681,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     }
 
     // ---------------------------------------------------------------- teardown
-    if (lane == 0) dbg_stage(3 + warp);
     __syncwarp();
     if ((warp == LOADK_WARP || warp == LOADV_WARP) && lane == 0 && *abort_flag) {
         // a wait gave up somewhere: give the loads this warp issued a moment (100 us in all) to land before the CTA's
@@ -730,7 +697,6 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     if (warp == MMA_WARP) {
         tc_fence_after();
         tmem_dealloc(tmem, TMEM_COLS);
-        if (lane == 0) dbg_stage(15);
     }
 }
 
@@ -755,8 +721,6 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int H, int box_ro
                              CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-static uint32_t* g_trace = nullptr;
-
 struct AttnCall {
     const void *q, *k, *v, *k_mean, *v_mean;
     AttnArgs a;
@@ -765,6 +729,7 @@ struct AttnCall {
 static int launch_attention(const AttnCall& c, int mode, cudaStream_t stream) {
     const AttnArgs& a = c.a;
     if (a.L <= 0 || a.H <= 0) return set_error(-1, "attention: L and H must be positive");
+    if (a.status == nullptr) return set_error(-2, "attention: the device status word is not available on this device");
     if (((uintptr_t)c.q | (uintptr_t)c.k | (uintptr_t)c.v | (uintptr_t)a.out) & 15)
         return set_error(-1, "attention: q, k, v, out must be 16-byte aligned");
     CUtensorMap tk, tv, tkm, tvm, tkr, tvr;
@@ -784,13 +749,8 @@ static int launch_attention(const AttnCall& c, int mode, cudaStream_t stream) {
     } else {
         tkr = tk; tvr = tv;
     }
-    static bool attr_set[3] = {false, false, false};
     auto kern = mode == 0 ? attention_kernel<0> : mode == 1 ? attention_kernel<1> : attention_kernel<2>;
-    if (!attr_set[mode]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_ALLOC);
-        if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
-        attr_set[mode] = true;
-    }
+    if ((rc = opt_in_shared_memory((const void*)kern, (int)SMEM_ALLOC))) return rc;
     kern<<<a.nq * a.H, NTHREADS, SMEM_ALLOC, stream>>>(tk, tv, tkm, tvm, tkr, tvr, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
@@ -807,7 +767,6 @@ static void fill_common(AttnArgs& a, int L, int H, float threshold) {
     a.tail_valid = L - (a.nb - 1) * BK;
     a.tail_log2 = log2f((float)a.tail_valid);
     a.status = device_status_ptr();
-    a.trace = g_trace;
 }
 
 static void fill_q(AttnCall& c) { c.a.q = static_cast<const __nv_bfloat16*>(c.q); }
@@ -888,18 +847,3 @@ extern "C" int es_compensate_fallback(const void* q, const void* k_mean, const v
     fill_q(c);
     return launch_attention(c, 2, (cudaStream_t)stream);
 }
-
-// Debugging aid: when `buffer` (device memory, es_debug_trace_words() 32-bit words, zeroed by the caller) is not NULL,
-// the attention kernels launched afterwards record clock stamps of their first CTAs' pipeline stages into it.
-extern "C" int es_debug_set_trace(void* buffer) {
-#ifdef ES_TRACE
-    es::g_trace = static_cast<uint32_t*>(buffer);
-    uint32_t* rep = buffer ? static_cast<uint32_t*>(buffer) + es::TRACE_CTAS * 2 * es::TRACE_ITERS * 8 : nullptr;
-    cudaMemcpyToSymbol(g_dbg_report, &rep, sizeof(rep));
-    return 0;
-#else
-    (void)buffer;
-    return es::set_error(-4, "es_debug_set_trace: this build has no trace code (compile with -DES_TRACE)");
-#endif
-}
-extern "C" int es_debug_trace_words(void) { return es::TRACE_CTAS * 2 * es::TRACE_ITERS * 8 + 512; }

@@ -61,24 +61,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 // second), short enough that a stuck pipeline returns quickly.
 constexpr uint64_t kWaitLimitNs = 500000000ull;
 
-#ifdef ES_TRACE
-// Debug builds only: a report area (host-mapped memory works, so the host can read it while a kernel is stuck).
-// Words [0, 256): last stage per SM; [256, 512): last timed-out wait per SM (code | CTA << 12).
-static __device__ uint32_t* g_dbg_report = nullptr;
-__device__ __forceinline__ uint32_t dbg_smid() { uint32_t r; asm volatile("mov.u32 %0, %%smid;" : "=r"(r)); return r; }
-__device__ __forceinline__ void dbg_stage(uint32_t stage) {
-    uint32_t* r = *reinterpret_cast<uint32_t* volatile*>(&g_dbg_report);
-    if (r) reinterpret_cast<volatile uint32_t*>(r)[dbg_smid() & 255] = (blockIdx.x << 4) | stage;
-}
-__device__ __forceinline__ void dbg_timeout(int code) {
-    uint32_t* r = *reinterpret_cast<uint32_t* volatile*>(&g_dbg_report);
-    if (r) reinterpret_cast<volatile uint32_t*>(r)[256 + (dbg_smid() & 255)] = (uint32_t)code | (blockIdx.x << 12);
-}
-#else
-__device__ __forceinline__ void dbg_stage(uint32_t) {}
-__device__ __forceinline__ void dbg_timeout(int) {}
-#endif
-
 // Bounded wait. `abort_flag` (shared memory) is set by the first wait of the CTA that gives up; later waits return at
 // once. The device status word is checked too, so once one CTA has given up the others stop waiting as well and the
 // kernel ends quickly instead of after one time limit per CTA.
@@ -108,7 +90,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             late = dt > (int64_t)kWaitLimitNs ? late + 1 : 0;
             if (late >= 2) {
                 *abort_flag = 1;
-                dbg_timeout(code);
                 atomicCAS(status, 0, code + 1000 * (int)(blockIdx.x % 100000));   // which wait, in which CTA
                 return false;
             }

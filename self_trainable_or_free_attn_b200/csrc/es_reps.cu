@@ -566,12 +566,7 @@ extern "C" int es_reps_metric(const void* q, float* gram_parts, float* gram, voi
     gram_kernel<<<dim3(H, nsplit), 256, 0, st>>>((const __nv_bfloat16*)q, gram_parts, L, H, rps, nsplit);
     ES_CHECK_LAUNCH("gram");
     const int smem = (2 * HD * 129 + HD) * (int)sizeof(float);
-    static bool attr = false;
-    if (!attr) {
-        cudaError_t e = cudaFuncSetAttribute(metric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
-        attr = true;
-    }
+    if (int rc = opt_in_shared_memory((const void*)metric_kernel, smem)) return rc;
     const float scale = 1.0f / sqrtf((float)HD);
     metric_kernel<<<H, 256, smem, st>>>(gram_parts, (__nv_bfloat16*)metric, gram, nsplit, scale * scale / (float)L);
     ES_CHECK_LAUNCH("metric");
@@ -591,12 +586,7 @@ extern "C" int es_reps_kmeans(const void* k, const void* v, const void* metric, 
     if (((uintptr_t)k | (uintptr_t)metric) & 15) return set_error(-1, "es_reps_kmeans: k and metric must be 16-byte aligned");
     if ((k_mean == nullptr) != (v_mean == nullptr)) return set_error(-1, "es_reps_kmeans: give both means or neither");
     const int nb = (L + 63) / 64;
-    static bool attr = false;
-    if (!attr) {
-        cudaError_t e = cudaFuncSetAttribute(kmeans_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, KM_SMEM);
-        if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
-        attr = true;
-    }
+    if (int rc = opt_in_shared_memory((const void*)kmeans_kernel, KM_SMEM)) return rc;
     kmeans_kernel<<<dim3((nb + KM_BLOCKS - 1) / KM_BLOCKS, H), 256, KM_SMEM, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)metric, (const __nv_bfloat16*)probes,
         (__nv_bfloat16*)k_rep, (__nv_bfloat16*)v_rep, log_counts, (__nv_bfloat16*)k_mean, (__nv_bfloat16*)v_mean, L, H,
@@ -647,12 +637,7 @@ extern "C" int es_reps_metric_static(const void* q, float* gram, void* metric, v
     gram_kernel<<<dim3(H, nsplit), 256, 0, st>>>((const __nv_bfloat16*)q, parts, L, H, rps, nsplit);
     ES_CHECK_LAUNCH("gram");
     const int smem = (2 * HD * 129 + HD) * (int)sizeof(float);
-    static bool attr = false;
-    if (!attr) {
-        cudaError_t e = cudaFuncSetAttribute(metric_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
-        attr = true;
-    }
+    if (int rc = opt_in_shared_memory((const void*)metric_kernel, smem)) return rc;
     const float scale = 1.0f / sqrtf((float)HD);
     metric_kernel<<<H, 256, smem, st>>>(parts, (__nv_bfloat16*)metric, gram, nsplit, scale * scale / (float)L);
     ES_CHECK_LAUNCH("metric");

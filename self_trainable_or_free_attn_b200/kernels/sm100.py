@@ -49,6 +49,7 @@ def set_kernel_timer(timer):
 
 def _timed(fn):
     name = fn.__name__
+    fn = N.device_guard(fn)
 
     def wrapper(*args, **kwargs):
         t = _timer
@@ -201,6 +202,7 @@ def full_step_scales(offset, lse, scale_exact, scale_skip, L):
                                          N.stream_ptr()), "full_step_scales")
 
 
+@_timed
 def pack_plan(keep, exact_bits):
     """Bit mask of the exactly computed blocks: keep (H, nq, nb) uint8 -> exact_bits (H, nq, NW) int32."""
     H, nq, nb = keep.shape
@@ -209,6 +211,7 @@ def pack_plan(keep, exact_bits):
             "pack_plan")
 
 
+@_timed
 def rebuild_plan(exact_bits, skip_bits, keep, counts, blocks, refine, refine_counts, means, mean_counts):
     """keep mask, sorted block list, refine list (padded with nb) and sorted list of the blocks left to their means
     (`means`, shaped as `blocks`), with the lengths of the last two, from the two bit masks of a plan."""
@@ -251,6 +254,7 @@ class Representatives:
         else:
             self._build(q, k, v, k_mean, v_mean)
 
+    @N.device_guard
     def _build(self, q, k, v, k_mean, v_mean):
         _cuda_bf16(q, k, v)
         assert q.shape == k.shape == v.shape == (self.L, self.H, self.D)

@@ -88,6 +88,7 @@ def _pad64(n):
     return -(-n // 64) * 64
 
 
+@N.device_guard
 def pool_fwd(q, k, v, blk_cnt, R):
     """(qr, kr [B,H,Lr_pad,D] router group means; qc, kc, vc [B,H,NBc_pad,D] block means)."""
     B, H, L, D = q.shape
@@ -101,6 +102,7 @@ def pool_fwd(q, k, v, blk_cnt, R):
     return qr, kr, qc, kc, vc
 
 
+@N.device_guard
 def router_scores(qr, kr, blk_cnt, R, row_norm=1):
     """Block scores [B, H, NB, NB] fp32 of the PSP router (diagnostic; `route` uses the same kernels)."""
     B, H, lr_pad, D = qr.shape
@@ -115,6 +117,7 @@ def router_scores(qr, kr, blk_cnt, R, row_norm=1):
     return scores
 
 
+@N.device_guard
 def global_topk(scores, budget):
     """Exact global top-`budget` of every (b, h) score matrix -> Selection."""
     B, H, nb, _ = scores.shape
@@ -130,6 +133,43 @@ def global_topk(scores, budget):
     return Selection(qp, qi, kp, ki)
 
 
+# ------------------------------------------------------------------------------------------- backward variant knobs
+# The reference has three generic fine-backward variants (0 / 1: dQ added with atomics, 2: a second q -> kv pass without
+# atomics; echosparse/vsa/dispatch.py:1-53) and bit options for its ThunderKittens backward (ops.py:171-177). This
+# library has one backward, the atomics-free two-pass form (their variant 2), so the knobs are accepted, validated the
+# same way and remembered, and change nothing: code written against the reference keeps importing and running.
+BWD_VARIANTS = (0, 1, 2)
+TK_BWD_OPTS = (0, 1, 2, 3, 16, 17, 18, 19)
+_knobs = {"bwd_variant": None, "tk_bwd_opts": None}
+
+
+def set_bwd_variant(v):
+    """Accepted for compatibility (None, 0, 1 or 2; anything else raises ValueError). The backward here is always the
+    two-pass, atomics-free one."""
+    if v is not None and v not in BWD_VARIANTS:
+        raise ValueError(f"set_bwd_variant takes None or one of {BWD_VARIANTS}; got {v!r}")
+    _knobs["bwd_variant"] = None if v is None else int(v)
+
+
+def resolve_bwd_variant(q, call=None):
+    """(variant, source) the way the reference reports it: this build always runs variant 2; `source` says whether a
+    per-call value, `set_bwd_variant` or nothing ("auto") asked for one."""
+    for value, source in ((call, "call"), (_knobs["bwd_variant"], "set_bwd_variant")):
+        if value is not None:
+            if value not in BWD_VARIANTS:
+                raise ValueError(f"{source}: the variant is one of {BWD_VARIANTS}; got {value!r}")
+            return 2, source
+    return 2, "auto"
+
+
+def set_tk_bwd_opts(v):
+    """Accepted for compatibility (None or one of the reference's option words). There is no ThunderKittens backward
+    in this build, so nothing changes."""
+    if v is not None and v not in TK_BWD_OPTS:
+        raise ValueError(f"set_tk_bwd_opts takes None or one of {TK_BWD_OPTS}; got {v!r}")
+    _knobs["tk_bwd_opts"] = v
+
+
 def budget_from_topk(nb, topk, budget):
     if budget is not None:
         return int(budget)
@@ -142,6 +182,7 @@ def _route(qr, kr, blk_cnt, R, budget, row_norm):
     return global_topk(router_scores(qr, kr, blk_cnt, R, row_norm), budget)
 
 
+@N.device_guard
 def route(q, k, blk_cnt, R=16, topk=None, budget=None, row_norm="paper"):
     """Standalone VSA2 PSP router + exact global top-k (stop-gradient)."""
     _check_tokens(q, k, k)
@@ -154,6 +195,7 @@ def route(q, k, blk_cnt, R=16, topk=None, budget=None, row_norm="paper"):
 _ROWS_POOL_R = 32
 
 
+@N.device_guard
 def block_scores(qc, kc, nb):
     """Original-VSA block scores [B, H, NB, NB] in the token dtype from the block means."""
     B, H, nbc_pad, D = qc.shape
@@ -163,6 +205,7 @@ def block_scores(qc, kc, nb):
     return scores
 
 
+@N.device_guard
 def row_topk(scores, topk):
     """Exactly min(topk, NB) kv blocks per query row of 16-bit scores [B, H, NB, NB] -> Selection."""
     B, H, nb, _ = scores.shape
@@ -177,6 +220,7 @@ def row_topk(scores, topk):
     return Selection(qp, qi, kp, ki)
 
 
+@N.device_guard
 def route_rows(q, k, blk_cnt, topk):
     """Standalone original-VSA router (stop-gradient): whole-block scores, exactly min(topk, NB) blocks per row."""
     _check_tokens(q, k, k)
@@ -185,6 +229,7 @@ def route_rows(q, k, blk_cnt, topk):
     return row_topk(block_scores(qc, kc, q.shape[2] // 64), topk)
 
 
+@N.device_guard
 def attn_fwd(q, k, v, ptr, idx, cnt):
     """(O, lse) of the list attention; q, k, v [B, H, L, D], lists over L / 64 blocks."""
     B, H, L, D = q.shape
@@ -229,6 +274,22 @@ def _bwd_q(q, k, v, dout, lse, delta, ptr, idx, cnt, add_dq=None, f32=False):
 
 
 # ------------------------------------------------------------------------------------------- split-KV scheduling
+def _want_nonneg_real(owner, field, value):
+    """Thresholds: a finite real number >= 0 (bool is not a number here). TypeError / ValueError as the reference raises."""
+    if type(value) is bool or not isinstance(value, (int, float)):
+        raise TypeError(f"{owner}.{field} takes a real number, not {type(value).__name__}")
+    if value != value or value in (math.inf, -math.inf) or value < 0:
+        raise ValueError(f"{owner}.{field} = {value!r}: expected a finite value >= 0")
+
+
+def _want_count(owner, field, value):
+    """Counts: a true int >= 1."""
+    if type(value) is bool or not isinstance(value, int):
+        raise TypeError(f"{owner}.{field} takes an int, not {type(value).__name__}")
+    if value < 1:
+        raise ValueError(f"{owner}.{field} = {value!r}: expected at least 1")
+
+
 @dataclass(frozen=True)
 class SplitPolicy:
     """Automatic per-direction choice of the lists worth splitting (reference: echosparse/vsa/ops.py:226-262).
@@ -245,20 +306,12 @@ class SplitPolicy:
     resident_ctas: Optional[int] = None
 
     def __post_init__(self):
-        for name in ("rel_mean", "tail_frac", "fwd_waves", "bwd_waves"):
-            v = getattr(self, name)
-            if isinstance(v, bool) or not isinstance(v, (int, float)):
-                raise TypeError(f"SplitPolicy.{name} must be a real number, got {type(v).__name__}")
-            if not math.isfinite(v) or v < 0:
-                raise ValueError(f"SplitPolicy.{name} must be finite and >= 0, got {v!r}")
-        for name in ("min_chunks", "max_task_waves", "resident_ctas"):
-            v = getattr(self, name)
-            if v is None and name == "resident_ctas":
-                continue
-            if isinstance(v, bool) or not isinstance(v, int):
-                raise TypeError(f"SplitPolicy.{name} must be an int, got {type(v).__name__}")
-            if v < 1:
-                raise ValueError(f"SplitPolicy.{name} must be >= 1, got {v!r}")
+        for field in ("rel_mean", "tail_frac", "fwd_waves", "bwd_waves"):
+            _want_nonneg_real("SplitPolicy", field, getattr(self, field))
+        _want_count("SplitPolicy", "min_chunks", self.min_chunks)
+        _want_count("SplitPolicy", "max_task_waves", self.max_task_waves)
+        if self.resident_ctas is not None:
+            _want_count("SplitPolicy", "resident_ctas", self.resident_ctas)
 
 
 @dataclass(frozen=True)
@@ -275,16 +328,21 @@ class SplitKV:
     policy: Optional[SplitPolicy] = None
 
     def __post_init__(self):
-        if not 1 <= int(self.chunk) <= 1 << 30:
-            raise ValueError(f"SplitKV.chunk must be in [1, 2**30], got {self.chunk}")
-        if int(self.max_scratch_bytes) < 0:
-            raise ValueError("SplitKV.max_scratch_bytes must be >= 0")
-        if self.policy is not None and not isinstance(self.policy, SplitPolicy):
-            raise TypeError("SplitKV.policy must be a SplitPolicy or None")
+        chunk, cap = int(self.chunk), int(self.max_scratch_bytes)
+        if chunk < 1 or chunk > 2 ** 30:
+            raise ValueError(f"SplitKV.chunk = {self.chunk}: a chunk holds between 1 and 2**30 blocks")
+        if cap < 0:
+            raise ValueError(f"SplitKV.max_scratch_bytes = {self.max_scratch_bytes}: a byte count cannot be negative")
+        if not (self.policy is None or isinstance(self.policy, SplitPolicy)):
+            raise TypeError(f"SplitKV.policy takes a SplitPolicy or None, not {type(self.policy).__name__}")
 
     @classmethod
     def auto(cls, chunk=64, fwd=True, bwd=True, max_scratch_bytes=64 << 20, policy=None):
-        return cls(chunk=chunk, fwd=fwd, bwd=bwd, max_scratch_bytes=max_scratch_bytes, policy=policy or SplitPolicy())
+        """The planner on the GPU decides per direction which lists to split (default thresholds of `SplitPolicy`);
+        forward partials limited to 64 MiB unless told otherwise."""
+        if policy is None:
+            policy = SplitPolicy()
+        return cls(chunk, fwd, bwd, max_scratch_bytes, policy)
 
 
 def split_slots(nnz, chunk, slot_bytes, max_bytes):
@@ -302,6 +360,7 @@ def split_resident(q, kind, policy=None):
     return torch.cuda.get_device_properties(q.device).multi_processor_count * _CTAS_PER_SM[(kind, q.shape[-1])]
 
 
+@N.device_guard
 def split_plan(ptr, chunk, max_slots, min_len=0, rel_mean=0.0, tail_frac=0.0, resident=1, budget=-1):
     """(tasks [NR + max_slots, 4], merges [max(1, min(NR, max_slots // 2)), 4], info [8]) int32 on the device."""
     B, H, n1 = ptr.shape
@@ -454,6 +513,7 @@ def _fuse_bwd(dout, of, oc, gate, blk_cnt, gate_act):
 
 class _Function(torch.autograd.Function):
     @staticmethod
+    @N.device_guard
     def forward(ctx, q, k, v, gate, blk_cnt, R, budget, row_norm, gate_act, sel_in, split):
         B, H, L, D = q.shape
         nb = L // 64
@@ -481,6 +541,7 @@ class _Function(torch.autograd.Function):
         return o, sel.q2k_ptr, sel.q2k_idx, sel.k2q_ptr, sel.k2q_idx
 
     @staticmethod
+    @N.device_guard
     def backward(ctx, dout, *unused):
         q, k, v, gate, blk_cnt = ctx.saved_tensors
         if ctx.inter is None:
@@ -500,6 +561,7 @@ class _Function(torch.autograd.Function):
         return (dq, dk, dv, dgate if ctx.has_gate else None) + (None,) * 7
 
 
+@N.device_guard
 def vsa2_attention(q, k, v, gate, blk_cnt, *, R=16, topk=None, budget=None, row_norm="paper", gate_act="tanh",
                    backend="auto", selection: Optional[Selection] = None, return_selection=False, split_kv=None):
     """Full VSA2 attention: O = O_fine + act(gate) * repeat(O_coarse).
@@ -529,6 +591,7 @@ def vsa2_attention(q, k, v, gate, blk_cnt, *, R=16, topk=None, budget=None, row_
     return o
 
 
+@N.device_guard
 def vsa_attention(q, k, v, blk_cnt, topk, *, weight=None, backend="auto", selection: Optional[Selection] = None,
                   return_selection=False, split_kv=None):
     """Original VSA attention (64-token blocks): O = O_fine + W * repeat(O_coarse) (reference: echosparse/vsa/ops.py:574-601).
@@ -559,6 +622,7 @@ def vsa_attention(q, k, v, blk_cnt, topk, *, weight=None, backend="auto", select
 
 class _FineFunction(torch.autograd.Function):
     @staticmethod
+    @N.device_guard
     def forward(ctx, q, k, v, blk_cnt, sel, split):
         of, lse = _fine_fwd(q, k, v, sel, blk_cnt, split)
         ctx.split = split
@@ -567,6 +631,7 @@ class _FineFunction(torch.autograd.Function):
         return of, lse
 
     @staticmethod
+    @N.device_guard
     def backward(ctx, dout, dlse):
         q, k, v, blk_cnt, of, lse, qp, qi, kp, ki = ctx.saved_tensors
         B, H, L, D = q.shape
@@ -577,6 +642,7 @@ class _FineFunction(torch.autograd.Function):
         return dq, dk, dv, None, None, None
 
 
+@N.device_guard
 def fine_block_sparse_attention(q, k, v, blk_cnt, selection: Selection, backend="auto", split_kv=None):
     """Diagnostic fine-only primitive (no coarse branch, no router). Returns (O_f, lse); query blocks without an edge and
     padded rows give O_f = 0 and lse = -inf."""

@@ -30,22 +30,21 @@ class RepTiers:
     mid_reps: int = 4
 
     def __post_init__(self):
-        for name in ("frac_full", "frac_mid"):
-            v = getattr(self, name)
-            if isinstance(v, bool) or not isinstance(v, (int, float)):
-                raise TypeError(f"RepTiers.{name} must be a real number, got {type(v).__name__}")
-            if not math.isfinite(v) or v < 0:
-                raise ValueError(f"RepTiers.{name} must be finite and >= 0, got {v!r}")
-        if self.frac_full + self.frac_mid > 1.0 + 1e-9:
-            raise ValueError(f"frac_full + frac_mid must be <= 1, got {self.frac_full} + {self.frac_mid}")
+        ops._want_nonneg_real("RepTiers", "frac_full", self.frac_full)
+        ops._want_nonneg_real("RepTiers", "frac_mid", self.frac_mid)
+        both = self.frac_full + self.frac_mid
+        if both > 1.0 + 1e-9:
+            raise ValueError(f"RepTiers: tiers A and B together take {both} of the pairs; at most 1")
         if self.mid_reps not in MID_REPS_OK:
-            raise ValueError(f"RepTiers.mid_reps must be one of {MID_REPS_OK}, got {self.mid_reps!r}")
+            raise ValueError(f"RepTiers.mid_reps = {self.mid_reps!r}: a block splits into one of {MID_REPS_OK} groups")
 
     def budgets(self, nb) -> Tuple[int, int]:
-        """(tier-A budget, tier-A-or-B budget) in pairs per (b, h), both clamped to NB * NB."""
-        nn = nb * nb
-        ba = min(nn, int(round(self.frac_full * nn)))
-        return ba, min(nn, max(ba, int(round((self.frac_full + self.frac_mid) * nn))))
+        """Pairs per (b, h) in tier A, and in tiers A and B together; never more than NB * NB, the second never less than
+        the first (reference: vsa2_rep/ops.py:76-81)."""
+        pairs = nb * nb
+        full = min(pairs, int(round(self.frac_full * pairs)))
+        full_or_mid = int(round((self.frac_full + self.frac_mid) * pairs))
+        return full, min(pairs, max(full, full_or_mid))
 
 
 @dataclass
@@ -102,6 +101,7 @@ def _topk_with_bits(scores, budget):
     return ops.Selection(qp, qi, kp, ki), bits
 
 
+@N.device_guard
 def route_tiers(q, k, blk_cnt, tiers: RepTiers = RepTiers(), *, R=16, row_norm="paper"):
     """VSA2's PSP router + exact global top-k at two budgets (stop-gradient)."""
     ops._check_tokens(q, k, k)
@@ -115,6 +115,7 @@ def route_tiers(q, k, blk_cnt, tiers: RepTiers = RepTiers(), *, R=16, row_norm="
     return TierSelection(sel_a.q2k_ptr, sel_a.q2k_idx, sel_a.k2q_ptr, sel_a.k2q_idx, bits_a, bits_ab)
 
 
+@N.device_guard
 def rep_build(k, v, blk_cnt, mid_reps):
     """Representative tables (k_mid, v_mid [B,H,mid_stride,D], k_tail, v_tail [B,H,tail_stride,D]): the group means of the
     64 / mid_reps-token groups and the block means of K and V over their valid tokens, rounded to the token dtype."""
@@ -175,6 +176,7 @@ def _tier_bwd(q, k, v, tab, dout, lse, delta, sel, blk_cnt, mid_reps, phases, ad
 
 class _TierFineFunction(torch.autograd.Function):
     @staticmethod
+    @N.device_guard
     def forward(ctx, q, k, v, blk_cnt, sel, mid_reps, phases):
         tab = rep_build(k, v, blk_cnt, mid_reps)
         of, lse = _tier_fwd(q, k, v, tab, sel, blk_cnt, mid_reps, phases)
@@ -184,6 +186,7 @@ class _TierFineFunction(torch.autograd.Function):
         return of, lse
 
     @staticmethod
+    @N.device_guard
     def backward(ctx, dout, dlse):
         q, k, v, blk_cnt, of, lse, *tab = ctx.saved_tensors
         B, H, L, D = q.shape
@@ -194,6 +197,7 @@ class _TierFineFunction(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None
 
 
+@N.device_guard
 def rep_fine_attention(q, k, v, blk_cnt, selection: TierSelection, mid_reps=4, phases=PHASE_ALL):
     """The three-tier fine branch alone (no coarse branch, no router). Returns (O_f, lse natural); padded rows and rows
     without a visible column give 0 and -inf. Gradients flow to the tokens through all three tiers: a representative's

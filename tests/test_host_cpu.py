@@ -47,14 +47,34 @@ def test_constructor_contract():
     with pytest.raises(AssertionError):
         EchoSparseAttention(dense_steps=1)
     attn = EchoSparseAttention(dense_layers=(0, 3))
-    assert attn.dense_layers == {0, 3} and attn.backend is None and attn.K is None and attn._states == {}
+    assert attn.dense_layers == {0, 3} and attn.backend is None and attn.K is None and not attn._states and len(attn._states) == 0
     attn.reset()
 
 
-def test_layer_state_shapes():
-    st = attention._LayerState(4152, 2, "cpu")
-    assert st.offset.shape == (33 * 128, 2) and float(st.offset[0, 0]) > 9e29
-    assert st.mass.shape == (2, 33, 65) and st.keep.shape == (2, 33, 65) and st.keep.dtype == torch.uint8
-    assert st.skip_bits.shape == (2, 33, 4) and int(st.skip_bits[0, 0, 0]) == -1
-    assert st.blocks.shape == (33, 2, 65) and st.refine.shape == (33, 2, 0) and not st.ready
-    assert attention._LayerState(75600, 1, "cpu").skip_bits.shape[-1] == 64
+def test_layer_record_shapes_and_plan_state():
+    """What a layer keeps between steps: two swapping offset buffers per branch and bit-mask plans."""
+    rec = attention._LayerRecord(4152, 2, "cpu", keep_lists=False)
+    br = rec.branch(0)
+    assert br.offset.shape == (33 * 128, 2) and float(br.offset[0, 0]) > 9e29 and br.offset is not br.next_offset
+    br.cur ^= 1
+    assert br.offset is br.buffers[1] and br.next_offset is br.buffers[0] and not br.ready
+    exact, skip = rec.plan(1)
+    assert len(rec.plans) == 2 and exact.shape == skip.shape == (2, 33, 4) and int(skip[0, 0, 0]) == -1
+    assert rec.offsets.keys() == {0} and rec.ready == set() and rec.offset(1).shape == (33 * 128, 2)
+    assert attention.plan_words(1182) == 64 and attention.plan_words(65) == 4 and attention.plan_words(8) == 4
+    lists = attention._Lists(4152, 2, "cpu", 32)
+    assert lists.keep.shape == (2, 33, 65) and lists.keep.dtype == torch.uint8 and lists.blocks.shape == (33, 2, 65)
+    assert lists.refine.shape == (33, 2, 32) and int(lists.refine[0, 0, 0]) == 65
+
+
+def test_state_table_views():
+    attn = EchoSparseAttention()
+    rec = attention._LayerRecord(4152, 2, "cpu", keep_lists=False)
+    rec.branch(0), rec.branch(1)
+    attn._states.put(3, rec)
+    assert sorted(attn._states) == [(0, 3), (1, 3)] and (1, 3) in attn._states and (2, 3) not in attn._states
+    assert attn._states[3] is rec and attn._states[(1, 3)].offset is rec.branches[1].offset
+    with pytest.raises(KeyError):
+        attn._states[(2, 3)]
+    attn._states.clear()
+    assert not attn._states
