@@ -88,7 +88,8 @@ int es_full_step_scales(const float* offset, float* lse, float* scale_exact, flo
 int es_pack_plan(const uint8_t* keep, int32_t* exact_bits, int32_t nw, int32_t H, int32_t nq, int32_t nb, void* stream);
 
 /* The two bit masks of a plan -> keep mask, sorted block list, refine list (padded with nb), mean list, with counts.
- * Replaces echosparse/kernels/sm120.py:299 `rebuild_plan`. blocks and means are (nq, H, nb). */
+ * Replaces echosparse/kernels/sm120.py:299 `rebuild_plan`. blocks and means are (nq, H, nb). means and mean_counts may
+ * both be NULL: the fused kernel of this library reads the block-mean columns from skip_bits, not from a list. */
 int es_rebuild_plan(const int32_t* exact_bits, const int32_t* skip_bits, int32_t nw, uint8_t* keep, int32_t* counts,
                     int32_t* blocks, int32_t* refine, int32_t rw, int32_t* refine_counts, int32_t* means,
                     int32_t* mean_counts, int32_t H, int32_t nq, int32_t nb, void* stream);

@@ -89,7 +89,7 @@ class _Lists:
 
 class _PlanScratch:
     """Scratch of the sparse path, shared by all layers: the block-probability map and its scales, the lists the current
-    call runs on, the lists the selection writes for the next step, and leftovers of `rebuild_plan` nothing reads."""
+    call runs on and the lists the selection writes for the next step."""
 
     def __init__(self, L, H, device, refine_width):
         nq, nb = cdiv(L, BM), cdiv(L, BK)
@@ -100,8 +100,6 @@ class _PlanScratch:
         self.lists = _Lists(L, H, device, refine_width)
         self.next_lists = _Lists(L, H, device, refine_width)
         self.refine_counts = torch.empty(nq, H, device=device, dtype=torch.int32)
-        self.means = torch.empty(nq, H, nb, device=device, dtype=torch.int32)
-        self.mean_counts = torch.empty(nq, H, device=device, dtype=torch.int32)
 
     # the names the reference's scratch object has
     keep = property(lambda self: self.lists.keep)
@@ -451,16 +449,15 @@ class EchoSparseAttention:
         if rec.keep_lists and index in rec.expanded and rec.expanded[index].refine.shape[-1] == ps.shape[2]:
             return rec.expanded[index]
         dst = ps.lists
-        self.K.rebuild_plan(exact, skip, dst.keep, dst.counts, dst.blocks, dst.refine, ps.refine_counts, ps.means,
-                            ps.mean_counts)
+        self.K.rebuild_plan(exact, skip, dst.keep, dst.counts, dst.blocks, dst.refine, ps.refine_counts)
         return dst
 
     def _plan_next(self, rec, ps, kept, flags, top, refined, L, sink, step):
         """Branch 0, end of a step: select the next step's blocks from the map in the workspace and pack them as a plan.
-        With several branches the other of two plans is written, because later branches of this step still read the
-        current one; a single branch rewrites its plan in place (unless the layer keeps expanded lists: the selection
-        reads the current keep mask while it writes the next one, so those always alternate)."""
-        index = 0 if rec.current is None else rec.current[0] ^ (len(rec.branches) > 1 or rec.keep_lists)
+        The other of the layer's two plans is written: later branches of this step still read the current one, the
+        selection reads the current keep mask while it writes the next, and the masks a step ran on stay readable until
+        the next step has run."""
+        index = 0 if rec.current is None else rec.current[0] ^ 1
         exact, skip = rec.plan(index)
         dst = rec.lists_of(index, ps.shape[2]) if rec.keep_lists else ps.next_lists
         self.K.select_blocks(ps.mass, kept, ps.scale_exact, ps.scale_skip, dst.keep, dst.counts, dst.blocks, flags, skip,

@@ -256,6 +256,143 @@ rebuild_kernel(const int* __restrict__ exact_bits, const int* __restrict__ skip_
     }
 }
 
+// ---------------------------------------------------------------------------------------------- one warp per (tile, head)
+// For up to 2048 kv blocks a whole (tile, head) fits the registers of one warp: lane l holds blocks 32 i + l. The K-th
+// largest key is then found the way the reference finds it (31 halvings of [0, 0x7F800001) on the int32 bit patterns,
+// triton_ops.py:43-54), each step one compare per held key and a warp sum: no shared memory, no atomics, no CTA barrier,
+// and every warp of a CTA works on a tile of its own. Word i of a bit mask is simply the ballot of round i.
+constexpr int SELW_WARPS = 8;
+
+template <int IPL>
+__device__ __forceinline__ int kth_largest_key_warp(const int (&key)[IPL], int K) {
+    int lo = 0, hi = 0x7F800001;
+#pragma unroll 1
+    for (int step = 0; step < 31; ++step) {
+        const int mid = lo + (hi - lo) / 2;
+        int c = 0;
+#pragma unroll
+        for (int i = 0; i < IPL; ++i) c += key[i] >= mid;
+        c = __reduce_add_sync(0xffffffffu, c);
+        if (c >= K) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+template <int IPL>
+__global__ void __launch_bounds__(SELW_WARPS * 32)
+select_warp_kernel(const float* __restrict__ map, const uint8_t* __restrict__ keep_prev,
+                   const float* __restrict__ scale_exact, const float* __restrict__ scale_skip,
+                   uint8_t* __restrict__ keep_out, int* __restrict__ counts, int* __restrict__ blocks,
+                   const int* __restrict__ flags, int* __restrict__ bits, int nw, int* __restrict__ refine, int rw, int K,
+                   int R, int nb, int L, int sink, int H, int nq) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * SELW_WARPS + (threadIdx.x >> 5);       // (head, tile) pairs in the map's order
+    if (unit >= nq * H) return;
+    const int h = unit / nq, t = unit - h * nq;
+    const size_t base = ((size_t)h * nq + t) * nb;
+    const int lo = (t * 128) / 64 - 1;
+    const int hi = (min((t + 1) * 128, L) - 1) / 64 + 1;
+    const float se = scale_exact[h * nq + t], ss = scale_skip[h * nq + t];
+    const bool fell_back = flags[t * H + h] != 0;
+    const unsigned below = (1u << lane) - 1u;
+
+    float raw[IPL];
+    int key[IPL];
+#pragma unroll
+    for (int i = 0; i < IPL; ++i) {
+        const int j = 32 * i + lane;
+        const bool valid = j < nb;
+        raw[i] = valid ? map[base + j] : 0.f;
+        const bool kept_before = valid && keep_prev[base + j] != 0;
+        // a tile that fell back to online softmax has no valid masses: keep its previous blocks first
+        float v = kept_before ? (fell_back ? INFINITY : raw[i] * se) : raw[i] * ss;
+        v = (v == v) ? v : 0.f;
+        v = (j >= sink) ? INFINITY : v;
+        key[i] = __float_as_int(valid ? v : -1.f);
+    }
+    const int thr = kth_largest_key_warp<IPL>(key, K);
+    // keep = value at or above the K-th largest (ties all kept), or forced: the tile's own blocks, one more on each side,
+    // and the sink. From here on key[] holds the refine candidates' keys: raw mass of the blocks not kept, -1 otherwise.
+    unsigned keep_w[IPL];
+    int nkeep = 0;
+    int* blist = blocks + ((size_t)t * H + h) * nb;
+#pragma unroll
+    for (int i = 0; i < IPL; ++i) {
+        const int j = 32 * i + lane;
+        const bool valid = j < nb;
+        // float comparison, as the reference compares values with the threshold value (negative keys are the invalid slots)
+        const bool keep = valid && (__int_as_float(key[i]) >= __int_as_float(thr) || (j >= lo && j <= hi) || j >= sink);
+        const unsigned b = __ballot_sync(0xffffffffu, keep);
+        keep_w[i] = b;
+        if (keep) blist[nkeep + __popc(b & below)] = j;
+        nkeep += __popc(b);
+        if (valid) keep_out[base + j] = keep ? 1 : 0;
+        float r = (raw[i] == raw[i]) ? raw[i] : 0.f;
+        key[i] = __float_as_int((valid && !keep) ? r : -1.f);
+    }
+    if (lane == 0) counts[t * H + h] = nkeep;
+    const int rthr = kth_largest_key_warp<IPL>(key, R);
+    // refine list: candidates at or above the R-th largest raw mass, ties cut in ascending block order
+    int* rlist = refine + ((size_t)t * H + h) * rw;
+    int* words = bits + ((size_t)h * nq + t) * nw;
+    int nref = 0;
+#pragma unroll
+    for (int i = 0; i < IPL; ++i) {
+        const int j = 32 * i + lane;
+        const bool cand = key[i] >= rthr && key[i] >= 0;
+        const unsigned c = __ballot_sync(0xffffffffu, cand);
+        const int pos = nref + __popc(c & below);
+        const bool ref = cand && pos < R;
+        const unsigned rb = __ballot_sync(0xffffffffu, ref);
+        if (ref && pos < rw) rlist[pos] = j;
+        nref += __popc(rb);
+        // bit set = the block-mean compensation skips the block: exact, refined, or past nb
+        const unsigned past = (32 * i + 31 < nb) ? 0u : (32 * i >= nb ? 0xffffffffu : ~((1u << (nb - 32 * i)) - 1u));
+        if (lane == 0 && i < nw) words[i] = (int)(keep_w[i] | rb | past);
+    }
+    for (int j = nref + lane; j < rw; j += 32) rlist[j] = nb;                    // padding
+    for (int w = IPL + lane; w < nw; w += 32) words[w] = -1;                      // words past the last block
+}
+
+// (exact bits, skip bits) -> keep mask, ascending block list, refine list; lane l expands round i's bit l. `means` may
+// be null (the kernels of this library take the block-mean columns from the skip bits, not from a list).
+template <int IPL>
+__global__ void __launch_bounds__(SELW_WARPS * 32)
+rebuild_warp_kernel(const int* __restrict__ exact_bits, const int* __restrict__ skip_bits, int nw,
+                    uint8_t* __restrict__ keep, int* __restrict__ counts, int* __restrict__ blocks,
+                    int* __restrict__ refine, int rw, int* __restrict__ refine_counts, int* __restrict__ means,
+                    int* __restrict__ mean_counts, int nb, int nq, int H) {
+    const int lane = threadIdx.x & 31;
+    const int unit = blockIdx.x * SELW_WARPS + (threadIdx.x >> 5);
+    if (unit >= nq * H) return;
+    const int h = unit / nq, t = unit - h * nq;
+    const int* ew = exact_bits + ((size_t)h * nq + t) * nw;
+    const int* sw = skip_bits + ((size_t)h * nq + t) * nw;
+    const size_t lbase = ((size_t)t * H + h) * nb, kbase = ((size_t)h * nq + t) * nb;
+    int* rlist = refine + ((size_t)t * H + h) * rw;
+    const unsigned below = (1u << lane) - 1u;
+    int nexact = 0, nref = 0, nmean = 0;
+#pragma unroll
+    for (int i = 0; i < IPL; ++i) {
+        if (32 * i >= nb) break;
+        const int j = 32 * i + lane;
+        const unsigned live = (32 * i + 31 < nb) ? 0xffffffffu : ((1u << (nb - 32 * i)) - 1u);
+        const unsigned e = (unsigned)ew[i] & live, sk = (unsigned)sw[i] & live;
+        const unsigned rf = sk & ~e, mn = ~sk & live;
+        if ((e >> lane) & 1u) blocks[lbase + nexact + __popc(e & below)] = j;
+        if ((rf >> lane) & 1u) { const int pos = nref + __popc(rf & below); if (pos < rw) rlist[pos] = j; }
+        if (means != nullptr && ((mn >> lane) & 1u)) means[lbase + nmean + __popc(mn & below)] = j;
+        if ((live >> lane) & 1u) keep[kbase + j] = (e >> lane) & 1u;
+        nexact += __popc(e); nref += __popc(rf); nmean += __popc(mn);
+    }
+    for (int j = min(nref, rw) + lane; j < rw; j += 32) rlist[j] = nb;
+    if (lane == 0) {
+        counts[t * H + h] = nexact;
+        refine_counts[t * H + h] = min(nref, rw);
+        if (mean_counts != nullptr) mean_counts[t * H + h] = nmean;
+    }
+}
+
 }  // namespace es
 
 using namespace es;
@@ -272,6 +409,25 @@ extern "C" int es_select_blocks(const float* mass, const uint8_t* keep_prev, con
     if (rw < r) return set_error(-1, "es_select_blocks: refine width smaller than r");
     if (rw > 0 && !refine) return set_error(-1, "es_select_blocks: null refine list");
     if (nw * 32 < nb) return set_error(-1, "es_select_blocks: skip_bits has fewer than nb bits per tile");
+    if (nb <= 2048) {
+        // one warp per (tile, head), blocks held 32 per round in registers
+        const int ipl = (nb + 31) / 32, units = nq * H;
+        const dim3 grid((units + SELW_WARPS - 1) / SELW_WARPS);
+#define ES_SELECTW_LAUNCH(N)                                                                                          \
+    select_warp_kernel<N><<<grid, SELW_WARPS * 32, 0, (cudaStream_t)stream>>>(mass, keep_prev, scale_exact, scale_skip, \
+                                                                               keep, counts, blocks, flags, skip_bits,  \
+                                                                               nw, refine, rw, k, r, nb, L, sink, H, nq)
+        if (ipl <= 8) ES_SELECTW_LAUNCH(8);
+        else if (ipl <= 16) ES_SELECTW_LAUNCH(16);
+        else if (ipl <= 24) ES_SELECTW_LAUNCH(24);
+        else if (ipl <= 32) ES_SELECTW_LAUNCH(32);
+        else if (ipl <= 40) ES_SELECTW_LAUNCH(40);
+        else if (ipl <= 48) ES_SELECTW_LAUNCH(48);
+        else ES_SELECTW_LAUNCH(64);
+#undef ES_SELECTW_LAUNCH
+        ES_CHECK_LAUNCH("select_blocks");
+        return 0;
+    }
     const int items = (nb + SEL_THREADS - 1) / SEL_THREADS;
 #define ES_SELECT_LAUNCH(N)                                                                                         \
     select_kernel<N><<<dim3(nq, H), SEL_THREADS, 0, (cudaStream_t)stream>>>(mass, keep_prev, scale_exact, scale_skip, \
@@ -299,10 +455,27 @@ extern "C" int es_pack_plan(const uint8_t* keep, int32_t* exact_bits, int32_t nw
 extern "C" int es_rebuild_plan(const int32_t* exact_bits, const int32_t* skip_bits, int32_t nw, uint8_t* keep,
                                int32_t* counts, int32_t* blocks, int32_t* refine, int32_t rw, int32_t* refine_counts,
                                int32_t* means, int32_t* mean_counts, int32_t H, int32_t nq, int32_t nb, void* stream) {
-    if (!exact_bits || !skip_bits || !keep || !counts || !blocks || !refine_counts || !means || !mean_counts)
+    if (!exact_bits || !skip_bits || !keep || !counts || !blocks || !refine_counts)
         return set_error(-1, "es_rebuild_plan: null pointer");
+    if ((means == nullptr) != (mean_counts == nullptr))
+        return set_error(-1, "es_rebuild_plan: give both the mean list and its counts, or neither");
+    if (rw > 0 && !refine) return set_error(-1, "es_rebuild_plan: null refine list");
     if (nb > SEL_THREADS * SEL_MAX_ITEMS) return set_error(-1, "es_rebuild_plan: more than 4096 kv blocks");
     if (nw * 32 < nb) return set_error(-1, "es_rebuild_plan: fewer than nb bits per tile");
+    if (nb <= 4096) {
+        const int ipl = (nb + 31) / 32, units = nq * H;
+        const dim3 grid((units + SELW_WARPS - 1) / SELW_WARPS);
+#define ES_REBUILDW_LAUNCH(N)                                                                                           \
+    rebuild_warp_kernel<N><<<grid, SELW_WARPS * 32, 0, (cudaStream_t)stream>>>(exact_bits, skip_bits, nw, keep, counts,  \
+                                                                                blocks, refine, rw, refine_counts,      \
+                                                                                means, mean_counts, nb, nq, H)
+        if (ipl <= 16) ES_REBUILDW_LAUNCH(16);
+        else if (ipl <= 64) ES_REBUILDW_LAUNCH(64);
+        else ES_REBUILDW_LAUNCH(128);
+#undef ES_REBUILDW_LAUNCH
+        ES_CHECK_LAUNCH("rebuild_plan");
+        return 0;
+    }
     const int items = (nb + SEL_THREADS - 1) / SEL_THREADS;
 #define ES_REBUILD_LAUNCH(N)                                                                                          \
     rebuild_kernel<N><<<dim3(nq, H), SEL_THREADS, 0, (cudaStream_t)stream>>>(exact_bits, skip_bits, nw, keep, counts,  \

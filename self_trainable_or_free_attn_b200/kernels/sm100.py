@@ -212,12 +212,14 @@ def pack_plan(keep, exact_bits):
 
 
 @_timed
-def rebuild_plan(exact_bits, skip_bits, keep, counts, blocks, refine, refine_counts, means, mean_counts):
-    """keep mask, sorted block list, refine list (padded with nb) and sorted list of the blocks left to their means
-    (`means`, shaped as `blocks`), with the lengths of the last two, from the two bit masks of a plan."""
+def rebuild_plan(exact_bits, skip_bits, keep, counts, blocks, refine, refine_counts, means=None, mean_counts=None):
+    """keep mask, sorted block list and refine list (padded with nb) with their lengths, from the two bit masks of a plan.
+    `means` (shaped as `blocks`) and `mean_counts` receive the sorted list of the blocks left to their means when given;
+    this library's fused kernel takes those columns from `skip_bits` itself, so its processor passes None."""
     H, nq, nb = keep.shape
     assert exact_bits.shape == skip_bits.shape and exact_bits.dtype == skip_bits.dtype == torch.int32
-    assert blocks.shape == means.shape == (nq, H, nb)
+    assert blocks.shape == (nq, H, nb) and (means is None or means.shape == blocks.shape)
+    assert (means is None) == (mean_counts is None)
     N.check(N.load().es_rebuild_plan(N.ptr(exact_bits), N.ptr(skip_bits), exact_bits.shape[-1], N.ptr(keep),
                                      N.ptr(counts), N.ptr(blocks), N.ptr(refine), refine.shape[-1],
                                      N.ptr(refine_counts), N.ptr(means), N.ptr(mean_counts), H, nq, nb,

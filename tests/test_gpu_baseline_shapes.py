@@ -111,7 +111,7 @@ def check_whole_heads(K, s, own_selection=True):
     if own_selection:
         want = R.select_blocks(s["mass_full"].cpu(), torch.ones(H, nq, nb, dtype=torch.uint8), s["se"].cpu(), s["ss"].cpu(),
                                s["flags_full"].cpu(), s["top"], s["refined"], L, s["rw"], sink=s["sink"])
-        _same_selection(tuple(x.cpu() for x in s["selection"]), want)
+        _same_selection(s["selection"], want)
         assert int(counts.min()) >= s["top"]
         if s["sink"] < nb:
             assert bool((keep[:, :, s["sink"]:] == 1).all()), "every tile keeps the sink blocks"
