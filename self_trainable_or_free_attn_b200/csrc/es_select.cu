@@ -279,7 +279,7 @@ __device__ __forceinline__ int kth_largest_key_warp(const int (&key)[IPL], int K
 }
 
 template <int IPL>
-__global__ void __launch_bounds__(SELW_WARPS * 32)
+__global__ void __launch_bounds__(SELW_WARPS * 32, IPL <= 40 ? 2 : 1)
 select_warp_kernel(const float* __restrict__ map, const uint8_t* __restrict__ keep_prev,
                    const float* __restrict__ scale_exact, const float* __restrict__ scale_skip,
                    uint8_t* __restrict__ keep_out, int* __restrict__ counts, int* __restrict__ blocks,
@@ -313,7 +313,9 @@ select_warp_kernel(const float* __restrict__ map, const uint8_t* __restrict__ ke
     const int thr = kth_largest_key_warp<IPL>(key, K);
     // keep = value at or above the K-th largest (ties all kept), or forced: the tile's own blocks, one more on each side,
     // and the sink. From here on key[] holds the refine candidates' keys: raw mass of the blocks not kept, -1 otherwise.
-    unsigned keep_w[IPL];
+    unsigned mine[(IPL + 31) / 32];          // this lane's keep bits, one per round
+#pragma unroll
+    for (int w = 0; w < (IPL + 31) / 32; ++w) mine[w] = 0;
     int nkeep = 0;
     int* blist = blocks + ((size_t)t * H + h) * nb;
 #pragma unroll
@@ -323,7 +325,7 @@ select_warp_kernel(const float* __restrict__ map, const uint8_t* __restrict__ ke
         // float comparison, as the reference compares values with the threshold value (negative keys are the invalid slots)
         const bool keep = valid && (__int_as_float(key[i]) >= __int_as_float(thr) || (j >= lo && j <= hi) || j >= sink);
         const unsigned b = __ballot_sync(0xffffffffu, keep);
-        keep_w[i] = b;
+        mine[i >> 5] |= (keep ? 1u : 0u) << (i & 31);
         if (keep) blist[nkeep + __popc(b & below)] = j;
         nkeep += __popc(b);
         if (valid) keep_out[base + j] = keep ? 1 : 0;
@@ -348,7 +350,8 @@ select_warp_kernel(const float* __restrict__ map, const uint8_t* __restrict__ ke
         nref += __popc(rb);
         // bit set = the block-mean compensation skips the block: exact, refined, or past nb
         const unsigned past = (32 * i + 31 < nb) ? 0u : (32 * i >= nb ? 0xffffffffu : ~((1u << (nb - 32 * i)) - 1u));
-        if (lane == 0 && i < nw) words[i] = (int)(keep_w[i] | rb | past);
+        const unsigned kb = __ballot_sync(0xffffffffu, (mine[i >> 5] >> (i & 31)) & 1u);
+        if (lane == 0 && i < nw) words[i] = (int)(kb | rb | past);
     }
     for (int j = nref + lane; j < rw; j += 32) rlist[j] = nb;                    // padding
     for (int w = IPL + lane; w < nw; w += 32) words[w] = -1;                      // words past the last block
