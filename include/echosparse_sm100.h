@@ -50,16 +50,19 @@ int es_sparse_attention(const void* q, const void* k, const void* v, const void*
                         float threshold, void* stream);
 
 /* Online-softmax attention over the block list for the tiles whose flag is set; writes out and lse of those tiles.
- * Replaces echosparse/kernels/triton_ops.py:237 `exact_fallback(q, k, v, out, counts, blocks, lse, flags)`. */
+ * Replaces echosparse/kernels/triton_ops.py:237 `exact_fallback(q, k, v, out, counts, blocks, lse, flags)`.
+ * tile_scratch: device scratch of ceil(L / 128) * H + 1 int32, or NULL. With it the flagged tiles are first listed (one
+ * small kernel) and one CTA per SM walks the list; without it one CTA per tile is launched and tests its own flag, which
+ * costs more than the work when a fraction of a percent of the tiles is flagged. The results are the same. */
 int es_exact_fallback(const void* q, const void* k, const void* v, void* out, const int32_t* counts,
                       const int32_t* blocks, int32_t nk, float* lse, const int32_t* flags, int32_t L, int32_t H,
-                      void* stream);
+                      int32_t* tile_scratch, void* stream);
 
 /* Block-mean compensation of the blocks not kept, for flagged tiles, in place on out and lse.
  * Replaces echosparse/kernels/triton_ops.py:285 `compensate_fallback(q, k_mean, v_mean, keep, lse, out, flags)`.
- * keep (H, nq, nb) uint8. */
+ * keep (H, nq, nb) uint8. tile_scratch: as for es_exact_fallback. */
 int es_compensate_fallback(const void* q, const void* k_mean, const void* v_mean, const uint8_t* keep, float* lse,
-                           void* out, const int32_t* flags, int32_t L, int32_t H, void* stream);
+                           void* out, const int32_t* flags, int32_t L, int32_t H, int32_t* tile_scratch, void* stream);
 
 /* Mean key and value of every 64-token block. Replaces echosparse/kernels/triton_ops.py:37 `block_means`. */
 int es_block_means(const void* k, const void* v, void* k_mean, void* v_mean, int32_t L, int32_t H, void* stream);

@@ -25,8 +25,8 @@ SIGNATURES = {
     "es_block_attention": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F, _P],
     "es_sparse_attention": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F,
                             _P],
-    "es_exact_fallback": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _P],
-    "es_compensate_fallback": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P],
+    "es_exact_fallback": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _I, _I, _P, _P],
+    "es_compensate_fallback": [_P, _P, _P, _P, _P, _P, _P, _I, _I, _P, _P],
     "es_block_means": [_P, _P, _P, _P, _I, _I, _P],
     "es_select_blocks": [_P, _P, _P, _P, _P, _P, _P, _P, _P, _I, _P, _I, _I, _I, _I, _I, _I, _P],
     "es_estimate_skipped": [_P, _P, _P, _P, _P, _P, _P, _P, _I, _I, _P],

@@ -92,6 +92,8 @@ struct AttnArgs {
     int tail_valid;              // tokens of the last block
     float tail_log2;             // log2(tail_valid)
     int nvirt, nref;             // mean iterations (128 blocks each), refine iterations (32 list entries each)
+    const int* tile_list;        // fallback modes: tiles to process (head * nq + tile), ascending, or null: every CTA tests its flag
+    const int* tile_count;       // entries of tile_list
     int* status;
 };
 
@@ -156,16 +158,16 @@ struct SchedIter {
     }
 };
 
+// One (query tile, head): `tile` = head * nq + query tile. `again`: the CTA has run a tile before (its barriers exist).
 template <int MODE>
-__global__ void __launch_bounds__(NTHREADS, 1)
-attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                 const __grid_constant__ CUtensorMap tmKm, const __grid_constant__ CUtensorMap tmVm,
-                 const __grid_constant__ CUtensorMap tmKr, const __grid_constant__ CUtensorMap tmVr, const AttnArgs a) {
+__device__ __forceinline__ void attention_tile(const CUtensorMap& tmK, const CUtensorMap& tmV, const CUtensorMap& tmKm,
+                                               const CUtensorMap& tmVm, const CUtensorMap& tmKr, const CUtensorMap& tmVr,
+                                               const AttnArgs& a, const int tile, const bool again) {
     constexpr bool FALLBACK = MODE == 1;       // online-softmax recomputation of flagged tiles
     constexpr bool COMPENSATE = MODE == 2;     // block-mean compensation of flagged tiles, added to out / lse in place
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // adjacent CTAs are adjacent query tiles of one head: their kv lists overlap in L2
-    const int qb = blockIdx.x % a.nq, h = blockIdx.x / a.nq;
+    // adjacent tile numbers are adjacent query tiles of one head: their kv lists overlap in L2
+    const int qb = tile % a.nq, h = tile / a.nq;
     const int th_idx = qb * a.H + h;
     if (FALLBACK || COMPENSATE) {
         if (a.flags[th_idx] == 0) return;          // uniform over the CTA, before anything is allocated
@@ -198,6 +200,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
 
     if (tid == 0) {
         if (base & 1023u) atomicCAS(a.status, 0, 901);   // the swizzled tiles need a 1024-byte aligned base
+        if (again) {
+            // a CTA that walks a list of tiles makes its barriers anew for every tile
+            for (uint64_t* b = &ctl->qfull; b <= &ctl->sweepbar; ++b) mbar_inval(smem_u32(b));
+        }
         mbar_init(smem_u32(&ctl->qfull), NSOFT);
         for (int i = 0; i < NSLOT; ++i) {
             mbar_init(smem_u32(&ctl->full[i]), 1);
@@ -222,7 +228,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     }
     if (warp == MMA_WARP) {
         tmem_alloc(smem_u32(&ctl->tmem_base), TMEM_COLS);
-        tmem_relinquish();
+        // a CTA that walks a tile list allocates again for its next tile, so it keeps its permit to allocate
+        if ((MODE == 0 || a.tile_list == nullptr) && !again) tmem_relinquish();
         tc_fence_before();
     }
     __syncthreads();
@@ -700,6 +707,58 @@ attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant_
     }
 }
 
+template <int MODE>
+__global__ void __launch_bounds__(NTHREADS, 1)
+attention_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                 const __grid_constant__ CUtensorMap tmKm, const __grid_constant__ CUtensorMap tmVm,
+                 const __grid_constant__ CUtensorMap tmKr, const __grid_constant__ CUtensorMap tmVr, const AttnArgs a) {
+    if (MODE == 0 || a.tile_list == nullptr) {
+        attention_tile<MODE>(tmK, tmV, tmKm, tmVm, tmKr, tmVr, a, (int)blockIdx.x, false);
+        return;
+    }
+    // fallback modes with a tile list: a grid of one CTA per SM walks the flagged tiles, instead of one CTA per tile of
+    // which all but a fraction of a percent would find their flag clear and leave
+    const int count = *a.tile_count;
+    bool again = false;
+    for (int e = blockIdx.x; e < count; e += gridDim.x) {
+        attention_tile<MODE>(tmK, tmV, tmKm, tmVm, tmKr, tmVr, a, a.tile_list[e], again);
+        again = true;
+        __syncthreads();
+    }
+}
+
+// Tiles whose flag is set, in ascending tile number (head * nq + tile): one CTA, ordered compaction by prefix sums.
+__global__ void __launch_bounds__(1024)
+flag_list_kernel(const int* __restrict__ flags, int nq, int H, int* __restrict__ list, int* __restrict__ count) {
+    __shared__ int warp_sum[32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int n = nq * H, per = (n + 1023) / 1024, b0 = tid * per;
+    int mine = 0;
+    for (int b = b0; b < min(b0 + per, n); ++b) mine += flags[(b % nq) * H + b / nq] != 0;
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    if (lane == 31) warp_sum[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        int w = warp_sum[lane];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, w, o);
+            if (lane >= o) w += v;
+        }
+        warp_sum[lane] = w;
+    }
+    __syncthreads();
+    int pos = incl - mine + (warp > 0 ? warp_sum[warp - 1] : 0);
+    for (int b = b0; b < min(b0 + per, n); ++b)
+        if (flags[(b % nq) * H + b / nq] != 0) list[pos++] = b;
+    if (tid == 1023) *count = pos;
+}
+
 // ---------------------------------------------------------------------------------------------- host side
 // Representative tables (H, rows, 128) bf16 viewed as dims {128 d, rows, H}; a box is 64 d x 4 rows (one block's four rows).
 static int make_rep_map(CUtensorMap* m, const void* ptr, int rows, int H) {
@@ -751,7 +810,20 @@ static int launch_attention(const AttnCall& c, int mode, cudaStream_t stream) {
     }
     auto kern = mode == 0 ? attention_kernel<0> : mode == 1 ? attention_kernel<1> : attention_kernel<2>;
     if ((rc = opt_in_shared_memory((const void*)kern, (int)SMEM_ALLOC))) return rc;
-    kern<<<a.nq * a.H, NTHREADS, SMEM_ALLOC, stream>>>(tk, tv, tkm, tvm, tkr, tvr, a);
+    int grid = a.nq * a.H;
+    if (mode != 0 && a.tile_list != nullptr) {
+        // the flagged tiles as a list, then one CTA per SM walking it
+        flag_list_kernel<<<1, 1024, 0, stream>>>(a.flags, a.nq, a.H, const_cast<int*>(a.tile_list),
+                                                 const_cast<int*>(a.tile_count));
+        cudaError_t e0 = cudaGetLastError();
+        if (e0 != cudaSuccess) return set_error(-2, cudaGetErrorString(e0));
+        count_launch();
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+            return set_error(-2, "attention: cannot read the SM count");
+        grid = sms < grid ? sms : grid;
+    }
+    kern<<<grid, NTHREADS, SMEM_ALLOC, stream>>>(tk, tv, tkm, tvm, tkr, tvr, a);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return set_error(-2, cudaGetErrorString(e));
     count_launch();
@@ -819,7 +891,7 @@ extern "C" int es_sparse_attention(const void* q, const void* k, const void* v, 
 
 extern "C" int es_exact_fallback(const void* q, const void* k, const void* v, void* out, const int32_t* counts,
                                  const int32_t* blocks, int32_t nk, float* lse, const int32_t* flags, int32_t L,
-                                 int32_t H, void* stream) {
+                                 int32_t H, int32_t* tile_scratch, void* stream) {
     if (!q || !k || !v || !out || !counts || !blocks || !lse || !flags)
         return set_error(-1, "es_exact_fallback: null pointer");
     AttnCall c{};
@@ -828,12 +900,14 @@ extern "C" int es_exact_fallback(const void* q, const void* k, const void* v, vo
     c.a.out = (__nv_bfloat16*)out; c.a.counts = counts; c.a.blocks = blocks; c.a.nk = nk;
     c.a.offset = lse; c.a.lse = lse; c.a.flags = const_cast<int32_t*>(flags); c.a.mass = nullptr;
     c.a.nvirt = 0; c.a.nref = 0;
+    if (tile_scratch) { c.a.tile_count = tile_scratch; c.a.tile_list = tile_scratch + 1; }
     fill_q(c);
     return launch_attention(c, 1, (cudaStream_t)stream);
 }
 
 extern "C" int es_compensate_fallback(const void* q, const void* k_mean, const void* v_mean, const uint8_t* keep,
-                                      float* lse, void* out, const int32_t* flags, int32_t L, int32_t H, void* stream) {
+                                      float* lse, void* out, const int32_t* flags, int32_t L, int32_t H,
+                                      int32_t* tile_scratch, void* stream) {
     if (!q || !k_mean || !v_mean || !keep || !lse || !out || !flags)
         return set_error(-1, "es_compensate_fallback: null pointer");
     AttnCall c{};
@@ -844,6 +918,7 @@ extern "C" int es_compensate_fallback(const void* q, const void* k_mean, const v
     c.a.offset = lse; c.a.lse = lse; c.a.flags = const_cast<int32_t*>(flags); c.a.mass = nullptr;
     c.a.keep = keep;
     c.a.nvirt = (c.a.nb + 127) / 128; c.a.nref = 0;
+    if (tile_scratch) { c.a.tile_count = tile_scratch; c.a.tile_list = tile_scratch + 1; }
     fill_q(c);
     return launch_attention(c, 2, (cudaStream_t)stream);
 }

@@ -136,6 +136,13 @@ estimate_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
         cp_wait<1>();
         __syncthreads();
         const uint32_t tile = smem_addr(tiles[ct & 1]);
+        // Lane l owns blocks 64 ct + 2 l, + 1 of the chunk in the map: their keep bytes and masses are requested here, before
+        // the products, so that the loads have landed when the estimates are ready (asked for one by one after the
+        // products, behind the branch on the keep byte, they were a chain of dependent round trips to L2).
+        const int c0 = ct * 64 + 2 * lane;
+        const bool in0 = tv && c0 < nb, in1 = tv && c0 + 1 < nb;
+        const uint8_t kp0 = in0 ? keep[mbase + c0] : (uint8_t)0, kp1 = in1 ? keep[mbase + c0 + 1] : (uint8_t)0;
+        const float old0 = in0 ? map[mbase + c0] : 0.f, old1 = in1 ? map[mbase + c0 + 1] : 0.f;
         float acc[8][4];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
@@ -148,7 +155,10 @@ estimate_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
                 Elt<__nv_bfloat16>::mma(acc[2 * np], afr[ks], b[0], b[1]);
                 Elt<__nv_bfloat16>::mma(acc[2 * np + 1], afr[ks], b[2], b[3]);
             }
-        // acc[i][0], acc[i][1]: row g, blocks 64 ct + 8 i + 2 tg, + 1; acc[i][2], acc[i][3]: row g + 8
+        // acc[i][0], acc[i][1]: row g, blocks 64 ct + 8 i + 2 tg, + 1; acc[i][2], acc[i][3]: row g + 8. After the sums over
+        // the 16 rows (the lanes with the same tg) every lane holds the estimates of blocks 8 i + 2 tg, + 1 for all i;
+        // the pair with i == g is the one this lane owns: 8 g + 2 tg = 2 lane.
+        float est0 = 0.f, est1 = 0.f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             float e[2];
@@ -164,20 +174,14 @@ estimate_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __rest
                 s2 += __shfl_xor_sync(0xffffffffu, s2, 16);
                 e[x] = s2 * inv_ns;
             }
-            if (g == 0 && tv) {
-#pragma unroll
-                for (int x = 0; x < 2; ++x) {
-                    const int cc = ct * 64 + i * 8 + 2 * tg + x;
-                    if (cc < nb) {
-                        if (keep[mbase + cc] != 0) {
-                            num += map[mbase + cc];
-                            den += e[x];
-                        } else {
-                            map[mbase + cc] = e[x];
-                        }
-                    }
-                }
-            }
+            if (i == g) { est0 = e[0]; est1 = e[1]; }
+        }
+        // kept blocks: their exact masses calibrate the estimates; the others receive their estimate
+        if (in0) {
+            if (kp0 != 0) { num += old0; den += est0; } else map[mbase + c0] = est0;
+        }
+        if (in1) {
+            if (kp1 != 0) { num += old1; den += est1; } else map[mbase + c0 + 1] = est1;
         }
         __syncthreads();
     }

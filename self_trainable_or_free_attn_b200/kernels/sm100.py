@@ -131,6 +131,18 @@ def sparse_attention(q, k, v, k_mean, v_mean, skip_bits, out, counts, blocks, of
     return out
 
 
+_tile_scratch = {}
+
+
+def _tile_list_scratch(flags):
+    """Device scratch for the list of flagged tiles (one int32 per tile and one for the count), kept per device and size."""
+    key = (flags.device, flags.numel())
+    buf = _tile_scratch.get(key)
+    if buf is None:
+        buf = _tile_scratch[key] = torch.empty(flags.numel() + 1, device=flags.device, dtype=torch.int32)
+    return buf
+
+
 @_timed
 def exact_fallback(q, k, v, out, counts, blocks, lse, flags):
     """Online-softmax attention over the block list, for the tiles whose fixed offset was too far off."""
@@ -139,8 +151,8 @@ def exact_fallback(q, k, v, out, counts, blocks, lse, flags):
     _cuda_bf16(q, k, v, out)
     _lists(L, H, counts, blocks)
     N.check(N.load().es_exact_fallback(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(counts), N.ptr(blocks),
-                                       blocks.shape[-1], N.ptr(lse), N.ptr(flags), L, H, N.stream_ptr()),
-            "exact_fallback")
+                                       blocks.shape[-1], N.ptr(lse), N.ptr(flags), L, H,
+                                       N.ptr(_tile_list_scratch(flags)), N.stream_ptr()), "exact_fallback")
 
 
 @_timed
@@ -151,7 +163,8 @@ def compensate_fallback(q, k_mean, v_mean, keep, lse, out, flags):
     nq, nb = _cdiv(L, BM), _cdiv(L, BK)
     assert keep.shape == (H, nq, nb) and keep.dtype == torch.uint8 and keep.is_contiguous()
     N.check(N.load().es_compensate_fallback(N.ptr(q), N.ptr(k_mean), N.ptr(v_mean), N.ptr(keep), N.ptr(lse), N.ptr(out),
-                                            N.ptr(flags), L, H, N.stream_ptr()), "compensate_fallback")
+                                            N.ptr(flags), L, H, N.ptr(_tile_list_scratch(flags)), N.stream_ptr()),
+            "compensate_fallback")
 
 
 @_timed

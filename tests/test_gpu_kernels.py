@@ -329,3 +329,39 @@ def test_mass_map_is_reproducible(K):
         K.block_attention(q, k, v, out, counts, blocks, offset, lse, flags, mass=mass)
         runs.append((out.clone(), lse.clone(), mass.clone()))
     assert all(torch.equal(a, b) for a, b in zip(*runs))
+
+
+def test_fallback_over_a_tile_list_equals_one_cta_per_tile(K):
+    """The recomputation and compensation kernels walk a list of the flagged tiles when given scratch for it (the kernel-set
+    module always gives it); without scratch every tile's CTA tests its own flag. Same bits either way, for no, some and
+    all tiles flagged; 195 tiles, so that with every tile flagged the CTAs of the list walk (one per SM) run several tiles."""
+    from self_trainable_or_free_attn_b200 import _native as N
+    L, H = 8256, 3
+    nq, nb = R.cdiv(L, 128), R.cdiv(L, 64)
+    q, k, v = _inputs(L, H, seed=21)
+    counts, blocks = _all_lists(L, H)
+    km = torch.empty(nb, H, 128, device=DEV, dtype=torch.bfloat16)
+    vm = torch.empty_like(km)
+    K.block_means(k, v, km, vm)
+    keep = (torch.rand(H, nq, nb, device=DEV) < 0.3).to(torch.uint8)
+    lib = N.load()
+    for pattern in ("none", "some", "all"):
+        flags = {"none": torch.zeros(nq, H), "some": (torch.arange(nq * H).view(nq, H) % 5 == 1).float(),
+                 "all": torch.ones(nq, H)}[pattern].to(DEV).to(torch.int32)
+        base_out = torch.randn(L, H, 128, device=DEV).to(torch.bfloat16)
+        base_lse = torch.full((nq * 128, H), 3.0, device=DEV)
+        got = []
+        for scratch in (True, False):
+            out, lse = base_out.clone(), base_lse.clone()
+            if scratch:
+                K.exact_fallback(q, k, v, out, counts, blocks, lse, flags)
+                K.compensate_fallback(q, km, vm, keep, lse, out, flags)
+            else:
+                N.check(lib.es_exact_fallback(N.ptr(q), N.ptr(k), N.ptr(v), N.ptr(out), N.ptr(counts), N.ptr(blocks), nb,
+                                              N.ptr(lse), N.ptr(flags), L, H, None, N.stream_ptr()), "exact_fallback")
+                N.check(lib.es_compensate_fallback(N.ptr(q), N.ptr(km), N.ptr(vm), N.ptr(keep), N.ptr(lse), N.ptr(out),
+                                                   N.ptr(flags), L, H, None, N.stream_ptr()), "compensate_fallback")
+            got.append((out, lse))
+        assert torch.equal(got[0][0], got[1][0]) and torch.equal(got[0][1], got[1][1]), pattern
+        if pattern == "none":
+            assert torch.equal(got[0][0], base_out) and torch.equal(got[0][1], base_lse)
