@@ -305,6 +305,89 @@ def vsa2_reference_arm(args, threads):
     print(json.dumps(line), flush=True)
 
 
+def vsa2_abba(args, local):
+    """One arm against the default in ABBA order inside one process (default, arm, arm, default), the way the reference's
+    benchmarks/vsa2_native_bench.py orders its four runs: ratios only come from inside one run, because separate runs
+    drift. Arms are the split-KV schedules. Per leg: CUDA-event medians of the forward and of forward + backward, and
+    SHA-256 digests of O, dQ, dK, dV, dgate. Verdict, worst first: FAIL (a non-finite value or a non-zero padded slot),
+    NONDETERMINISTIC (the two default legs differ: every kernel here has one owner per output row, so they must not),
+    OVER_TOL (an output of the arm is further from the default than --abba-tol in relative L2), WITHIN_TOL, IDENTICAL."""
+    import hashlib
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    from self_trainable_or_free_attn_b200 import _native, vsa
+    from self_trainable_or_free_attn_b200.vsa import ops, workloads
+    sh = VSA2_SHAPE
+    heads = min(args.heads, sh["heads"]) if args.heads else sh["heads"]
+    q, k, v, gate, dout, lay = workloads.train_inputs(sh["grid"], heads, device=device)
+    cnt = lay.blk_cnt.to(device)
+    sel, nb = workloads.selection(args.skew, sh["grid"], heads, sh["topk"], device)
+    arms = {"baseline": None, "split_auto": vsa.SplitKV.auto(), "split_manual": vsa.SplitKV(chunk=64)}
+    valid = (torch.arange(q.shape[2], device=device) % 64 < cnt.repeat_interleave(64))[None, None, :, None]
+
+    def leg(split):
+        def fwd():
+            with torch.no_grad():
+                return vsa.vsa2_attention(q, k, v, gate, cnt, R=16, selection=sel, split_kv=split)
+
+        def both():
+            leaves = [x.detach().requires_grad_(True) for x in (q, k, v, gate)]
+            o = vsa.vsa2_attention(*leaves, cnt, R=16, selection=sel, split_kv=split)
+            return (o.detach(),) + torch.autograd.grad(o, leaves, dout)
+
+        def median_ms(fn):
+            for _ in range(args.warmup):
+                fn()
+            ts = []
+            for _ in range(args.steps):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                fn()
+                b.record()
+                torch.cuda.synchronize()
+                ts.append(a.elapsed_time(b))
+            return statistics.median(ts), (max(ts) - min(ts))
+        f_ms, f_spread = median_ms(fwd)
+        fb_ms, fb_spread = median_ms(both)
+        outs = both()
+        torch.cuda.synchronize()
+        finite = all(bool(torch.isfinite(t.float()).all()) for t in outs)
+        padding = all(bool((t.float() * (~valid if t.dim() == 4 else ~valid[..., 0]) == 0).all()) for t in outs)
+        digests = [hashlib.sha256(t.contiguous().cpu().view(torch.uint8).numpy().tobytes()).hexdigest()[:16] for t in outs]
+        return {"fwd_ms": f_ms, "fwd_spread_ms": f_spread, "f_plus_b_ms": fb_ms, "f_plus_b_spread_ms": fb_spread,
+                "b_estimate_ms": fb_ms - f_ms, "finite": finite, "padding_zero": padding, "digests": digests}, outs
+
+    order = ("default", "arm", "arm", "default")
+    legs, tensors = [], []
+    for name in order:
+        r, outs = leg(None if name == "default" else arms[args.abba])
+        legs.append(dict(r, leg=name))
+        tensors.append([t.float().cpu() for t in outs])
+    names = ("o", "dq", "dk", "dv", "dgate")
+    rel = lambda a, b: float((a - b).norm() / b.norm().clamp(min=1e-30))
+    arm_vs_default = {n: max(rel(tensors[1][i], tensors[0][i]), rel(tensors[2][i], tensors[3][i])) for i, n in enumerate(names)}
+    aa = {n: rel(tensors[0][i], tensors[3][i]) for i, n in enumerate(names)}
+    if not all(l["finite"] and l["padding_zero"] for l in legs):
+        verdict = "FAIL"
+    elif legs[0]["digests"] != legs[3]["digests"]:
+        verdict = "NONDETERMINISTIC"
+    elif max(arm_vs_default.values()) > args.abba_tol:
+        verdict = "OVER_TOL"
+    elif legs[1]["digests"] == legs[0]["digests"] and legs[2]["digests"] == legs[0]["digests"]:
+        verdict = "IDENTICAL"
+    else:
+        verdict = "WITHIN_TOL"
+    d_f = statistics.mean([legs[0]["fwd_ms"], legs[3]["fwd_ms"]])
+    d_fb = statistics.mean([legs[0]["f_plus_b_ms"], legs[3]["f_plus_b_ms"]])
+    a_f = statistics.mean([legs[1]["fwd_ms"], legs[2]["fwd_ms"]])
+    a_fb = statistics.mean([legs[1]["f_plus_b_ms"], legs[2]["f_plus_b_ms"]])
+    print(json.dumps({"schema": "vsa2-abba/1", "note": "measurement only: medians, spreads, ratios and errors",
+                      "arm": args.abba, "config": vsa2_config(args), "order": order, "legs": legs,
+                      "ratio_arm_over_default": {"fwd": a_f / d_f, "f_plus_b": a_fb / d_fb},
+                      "rel_l2_arm_vs_default": arm_vs_default, "rel_l2_default_vs_default": aa, "tolerance": args.abba_tol,
+                      "verdict": verdict, "device_status": _native.device_status()}), flush=True)
+
+
 def vsa2_arm(args, rank, world, local, threads):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA GPU; there is no CPU fallback of the product path")
@@ -462,6 +545,9 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer (end to end) measurement")
     ap.add_argument("--skew", default="uniform", help="vsa2_train: shape of the selection (vsa/workloads.py CASES)")
     ap.add_argument("--split", default="none", choices=["none", "auto", "manual"], help="vsa2_train: split-KV scheduling")
+    ap.add_argument("--abba", default=None, choices=["baseline", "split_auto", "split_manual"],
+                    help="vsa2_train: time this arm against the default in ABBA order and compare their outputs")
+    ap.add_argument("--abba-tol", type=float, default=1e-2, help="relative L2 an arm's outputs may differ from the default's")
     ap.add_argument("--threshold", type=float, default=60.0, help="flag threshold on |log2 row sum| (reference: 60)")
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -477,6 +563,8 @@ def main():
     if args.impl == "reference" and rank != 0:
         return
     threads = os.cpu_count() or 1
+    if args.workload == "vsa2_train" and args.abba:
+        return vsa2_abba(args, local) if rank == 0 else None
     if args.workload == "vsa2_train":
         return vsa2_reference_arm(args, threads) if args.impl == "reference" else vsa2_arm(args, rank, world, local, threads)
     grid, heads_all, branches, density, text = synthetic.WORKLOADS[args.workload]

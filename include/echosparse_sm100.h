@@ -28,6 +28,11 @@ long long es_launch_count(void);
  * (code of the bounded in-kernel wait that gave up) + 1000 * (its CTA index): that kernel returned early, its outputs are
  * invalid, and attention kernels launched before the word is read return at once. */
 int es_device_status(int32_t* status_out);
+/* Self test of that mechanism (no counterpart in the reference): launches one warp that waits on a barrier nobody arrives
+ * on, with a limit of limit_us microseconds (1 .. 100000). The wait gives up the way a wait of the attention kernels does:
+ * the kernel returns and the status word receives code 777. Nothing faults or hangs; read the word with es_device_status
+ * afterwards, or the attention kernels of this device stay switched off. */
+int es_selftest_wait_timeout(int32_t limit_us, void* stream);
 
 /* Exact attention over a list of 64-token blocks at a fixed softmax offset, with per-block masses.
  * Replaces echosparse/kernels/block_attention.py:327 `block_attention(q, k, v, out, counts, blocks, offset, lse, flags,

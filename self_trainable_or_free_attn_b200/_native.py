@@ -22,6 +22,7 @@ SIGNATURES = {
     "es_abi_version": [],
     "es_launch_count": [],
     "es_device_status": [_P],
+    "es_selftest_wait_timeout": [_I, _P],
     "es_block_attention": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F, _P],
     "es_sparse_attention": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F,
                             _P],

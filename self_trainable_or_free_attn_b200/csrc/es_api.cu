@@ -1,5 +1,6 @@
 // Library-wide pieces of the C ABI: last-error text, device status word, launch counter, tensor-map encoder.
 #include "es_api_internal.h"
+#include "es_ptx.cuh"
 
 #include <atomic>
 #include <cstdio>
@@ -85,7 +86,30 @@ int encode_tensor_map(CUtensorMap* m, CUtensorMapDataType dt, uint32_t rank, voi
     return 0;
 }
 
+// A wait that nothing ends: one warp waits on a barrier nobody arrives on, with a short limit. It takes the same path
+// as a wait of the attention kernels that runs out: the code goes to the status word, the kernel returns.
+__global__ void selftest_wait_kernel(int* status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncwarp();
+    mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 777, 0, limit_ns);
+}
+
 }  // namespace es
+
+extern "C" int es_selftest_wait_timeout(int32_t limit_us, void* stream) {
+    if (limit_us < 1 || limit_us > 100000) return es::set_error(-1, "es_selftest_wait_timeout: limit must be 1 .. 100000 us");
+    int* st = es::device_status_ptr();
+    if (!st) return es::set_error(-2, "es_selftest_wait_timeout: the device status word is not available");
+    es::selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(st, (unsigned long long)limit_us * 1000ull);
+    ES_CHECK_LAUNCH("selftest_wait");
+    return 0;
+}
 
 extern "C" const char* es_last_error(void) { return es::g_error; }
 

@@ -68,7 +68,7 @@ constexpr uint64_t kWaitLimitNs = 500000000ull;
 // once. The device status word is checked too, so once one CTA has given up the others stop waiting as well and the
 // kernel ends quickly instead of after one time limit per CTA.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code, int spins = 0) {
+                                          int code, int spins = 0, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_test_wait(bar, parity)) return true;      // the common case: the phase is already complete
     // `spins` > 0: poll with the non-blocking test first. A thread suspended in try_wait was seen to resume 400 to 600
     // clocks after the phase completed; a polling one sees it within a round trip to the barrier, but takes issue slots
@@ -90,7 +90,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             // signed difference, and two readings in a row past the limit: a single inconsistent reading of the
             // 64-bit timer (its halves are not updated together on every part) must not end a healthy wait
             const int64_t dt = (int64_t)global_timer_ns() - t0;
-            late = dt > (int64_t)kWaitLimitNs ? late + 1 : 0;
+            late = dt > (int64_t)limit_ns ? late + 1 : 0;
             if (late >= 2) {
                 *abort_flag = 1;
                 atomicCAS(status, 0, code + 1000 * (int)(blockIdx.x % 100000));   // which wait, in which CTA
