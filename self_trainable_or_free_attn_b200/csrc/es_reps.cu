@@ -119,37 +119,65 @@ gram_kernel(const __nv_bfloat16* __restrict__ q, float* __restrict__ parts, int 
 }
 
 // ------------------------------------------------------------------------------------------------ metric
-// G = (sum of partials) * scale^2 / L, regularised, then right-looking Cholesky with clamped pivots
-// (representatives.py:49-63, 163-165). One CTA per head; the matrix lives in shared memory.
+// Sum of the Gram partials of a head, scaled: parts[h][0] <- norm * sum_p parts[h][p], in the fixed order the sums have
+// always been taken in (four running sums over p % 4, then (s0 + s1) + (s2 + s3)). Sixteen CTAs per head, so that the
+// reduction of the 2 MB of partials is not one CTA's chain of loads (with a handful of heads per GPU it was).
+__global__ void __launch_bounds__(256)
+gram_reduce_kernel(float* __restrict__ parts, int nsplit, float norm) {
+    const int h = blockIdx.x, e0 = (blockIdx.y * 256 + threadIdx.x) * 4;
+    float* src = parts + (size_t)h * nsplit * HD * HD + e0;
+    float4 s4[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) s4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    int p = 0;
+    for (; p + 4 <= nsplit; p += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const float4 x = *reinterpret_cast<const float4*>(src + (size_t)(p + u) * HD * HD);
+            s4[u].x += x.x; s4[u].y += x.y; s4[u].z += x.z; s4[u].w += x.w;
+        }
+    }
+    for (int u = 0; p < nsplit; ++p, ++u) {
+        const float4 x = *reinterpret_cast<const float4*>(src + (size_t)p * HD * HD);
+        s4[u].x += x.x; s4[u].y += x.y; s4[u].z += x.z; s4[u].w += x.w;
+    }
+    float4 r;
+    r.x = ((s4[0].x + s4[1].x) + (s4[2].x + s4[3].x)) * norm;
+    r.y = ((s4[0].y + s4[1].y) + (s4[2].y + s4[3].y)) * norm;
+    r.z = ((s4[0].z + s4[1].z) + (s4[2].z + s4[3].z)) * norm;
+    r.w = ((s4[0].w + s4[1].w) + (s4[2].w + s4[3].w)) * norm;
+    *reinterpret_cast<float4*>(src) = r;              // the slot of split 0: only this thread reads or writes these elements
+}
+
+// G (from gram_reduce_kernel) regularised, then its Cholesky factor with clamped pivots (representatives.py:49-63,
+// 163-165), blocked: per panel of 16 columns one warp factors the 16 x 16 diagonal block in registers (a lane per row,
+// the pivot row's values by shuffle), every row below solves its 16 entries against that block, and the trailing matrix
+// takes the rank-16 update: three barriers per panel, 24 in all, against two per column in the unblocked form. One CTA
+// per head; the matrix lives in shared memory.
+constexpr int CH_PANEL = 16;
 __global__ void __launch_bounds__(256)
 metric_kernel(const float* __restrict__ parts, __nv_bfloat16* __restrict__ metric, float* __restrict__ gram_out,
-              int nsplit, float norm) {
+              int nsplit) {
     extern __shared__ float sm[];
     float* A = sm;                 // [128][129]
     float* Lm = A + HD * 129;      // [128][129]
-    float* lj = Lm + HD * 129;     // [128]
+    float* sq = Lm + HD * 129;     // [128] square roots of the clamped pivots
     __shared__ float red[8];
     __shared__ float s_eps, s_diag;
-    const int h = blockIdx.x, tid = threadIdx.x;
-    for (int e = tid; e < HD * HD; e += 256) {
-        // four running sums over the splits p % 4 (independent loads in flight), combined in a fixed order
-        float s4[4] = {0.f, 0.f, 0.f, 0.f};
-        const float* src = parts + (size_t)h * nsplit * HD * HD + e;
-        int p = 0;
-        for (; p + 4 <= nsplit; p += 4) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u) s4[u] += src[(size_t)(p + u) * HD * HD];
-        }
-        for (int u = 0; p < nsplit; ++p, ++u) s4[u] += src[(size_t)p * HD * HD];
-        const float s = (s4[0] + s4[1]) + (s4[2] + s4[3]);
-        A[(e >> 7) * 129 + (e & 127)] = s * norm;
-        Lm[(e >> 7) * 129 + (e & 127)] = 0.f;
+    const int h = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const float* src = parts + (size_t)h * nsplit * HD * HD;
+    for (int e = tid * 4; e < HD * HD; e += 1024) {
+        const float4 x = *reinterpret_cast<const float4*>(src + e);
+        float* dst = A + (e >> 7) * 129 + (e & 127);
+        dst[0] = x.x; dst[1] = x.y; dst[2] = x.z; dst[3] = x.w;
+        float* dl = Lm + (e >> 7) * 129 + (e & 127);
+        dl[0] = 0.f; dl[1] = 0.f; dl[2] = 0.f; dl[3] = 0.f;
     }
     __syncthreads();
     float dg = tid < HD ? A[tid * 129 + tid] : 0.f;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, o);
-    if ((tid & 31) == 0) red[tid >> 5] = dg;
+    if (lane == 0) red[warp] = dg;
     __syncthreads();
     if (tid == 0) s_diag = (((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]))) / HD;
     __syncthreads();
@@ -161,27 +189,68 @@ metric_kernel(const float* __restrict__ parts, __nv_bfloat16* __restrict__ metri
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) dg += __shfl_xor_sync(0xffffffffu, dg, o);
     __syncthreads();
-    if ((tid & 31) == 0) red[tid >> 5] = dg;
+    if (lane == 0) red[warp] = dg;
     __syncthreads();
     if (tid == 0)
         s_eps = (((red[0] + red[1]) + (red[2] + red[3])) + ((red[4] + red[5]) + (red[6] + red[7]))) / HD * 1e-12f;
     __syncthreads();
-    for (int j = 0; j < HD; ++j) {
-        if (tid < HD) {
-            const float piv = fmaxf(A[j * 129 + j], s_eps);
-            const float v = tid >= j ? A[tid * 129 + j] / sqrtf(piv) : 0.f;
-            lj[tid] = v;
-            Lm[tid * 129 + j] = v;
+    const float eps = s_eps;
+    for (int j0 = 0; j0 < HD; j0 += CH_PANEL) {
+        // (1) the diagonal block: lane i (and its duplicate i + 16) holds row j0 + i of the block
+        if (warp == 0) {
+            const int i = lane & 15, r = j0 + i;
+            float a[CH_PANEL];
+#pragma unroll
+            for (int c = 0; c < CH_PANEL; ++c) a[c] = A[r * 129 + j0 + c];
+#pragma unroll
+            for (int j = 0; j < CH_PANEL; ++j) {
+                const float root = sqrtf(fmaxf(__shfl_sync(0xffffffffu, a[j], j), eps));
+                const float l = i >= j ? a[j] / root : 0.f;
+                a[j] = l;
+                if (lane == j) sq[j0 + j] = root;
+#pragma unroll
+                for (int c = j + 1; c < CH_PANEL; ++c) {
+                    const float lc = __shfl_sync(0xffffffffu, l, c);
+                    if (i >= c) a[c] -= l * lc;
+                }
+            }
+            if (lane < 16) {
+#pragma unroll
+                for (int c = 0; c < CH_PANEL; ++c) Lm[r * 129 + j0 + c] = c <= i ? a[c] : 0.f;
+            }
         }
         __syncthreads();
-        // A -= lj lj^T on the lower triangle of the trailing block, the only part later columns read: two threads per
-        // row r > j, columns j + 1 .. r alternating between them
+        // (2) the rows below: L[r][j0 + j] = (A[r][j0 + j] - sum_{k < j} L[r][j0 + k] L[j0 + j][j0 + k]) / root_j
+        if (tid < HD && tid >= j0 + CH_PANEL) {
+            float x[CH_PANEL];
+#pragma unroll
+            for (int c = 0; c < CH_PANEL; ++c) x[c] = A[tid * 129 + j0 + c];
+#pragma unroll
+            for (int j = 0; j < CH_PANEL; ++j) {
+                float sacc = x[j];
+#pragma unroll
+                for (int k2 = 0; k2 < j; ++k2) sacc -= x[k2] * Lm[(j0 + j) * 129 + j0 + k2];
+                x[j] = sacc / sq[j0 + j];
+            }
+#pragma unroll
+            for (int c = 0; c < CH_PANEL; ++c) Lm[tid * 129 + j0 + c] = x[c];
+        }
+        __syncthreads();
+        // (3) A -= L_panel L_panel^T on the lower triangle of the trailing block: two threads per row, columns alternating
         {
             const int r = tid >> 1;
-            if (r > j) {
-                const float lr = lj[r];
+            if (r >= j0 + CH_PANEL) {
+                float lr[CH_PANEL];
+#pragma unroll
+                for (int k2 = 0; k2 < CH_PANEL; ++k2) lr[k2] = Lm[r * 129 + j0 + k2];
                 float* row = A + r * 129;
-                for (int c = j + 1 + (tid & 1); c <= r; c += 2) row[c] -= lr * lj[c];
+                for (int c = j0 + CH_PANEL + (tid & 1); c <= r; c += 2) {
+                    const float* lc = Lm + c * 129 + j0;
+                    float sacc = row[c];
+#pragma unroll
+                    for (int k2 = 0; k2 < CH_PANEL; ++k2) sacc -= lr[k2] * lc[k2];
+                    row[c] = sacc;
+                }
             }
         }
         __syncthreads();
@@ -221,7 +290,8 @@ __global__ void __launch_bounds__(256, 2)
 kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
               const __nv_bfloat16* __restrict__ metric, const __nv_bfloat16* __restrict__ probes,
               __nv_bfloat16* __restrict__ k4, __nv_bfloat16* __restrict__ v4, float* __restrict__ c4,
-              __nv_bfloat16* __restrict__ km, __nv_bfloat16* __restrict__ vm, int L, int H, int nb4, int iters) {
+              __nv_bfloat16* __restrict__ km, __nv_bfloat16* __restrict__ vm, int L, int H, int nb4, int iters,
+              int blocks_per_cta) {
     extern __shared__ __align__(16) uint8_t raw[];
     __nv_bfloat16* sM = reinterpret_cast<__nv_bfloat16*>(raw);                     // [128][MS] the head's metric
     __nv_bfloat16* sK = sM + 128 * MS;                                             // [64][KS]
@@ -259,7 +329,7 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
             pa[ks][3] = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16 + 8));
         }
     }
-  for (int j = blockIdx.x * KM_BLOCKS; j < min(nb, (int)(blockIdx.x + 1) * KM_BLOCKS); ++j) {
+  for (int j = blockIdx.x * blocks_per_cta; j < min(nb, (int)(blockIdx.x + 1) * blocks_per_cta); ++j) {
     const int nvalid = min(L - j * 64, 64);
     __syncthreads();                       // the previous block's readers of the shared tiles are done
     // K tile (rows past L are zero)
@@ -568,7 +638,9 @@ extern "C" int es_reps_metric(const void* q, float* gram_parts, float* gram, voi
     const int smem = (2 * HD * 129 + HD) * (int)sizeof(float);
     if (int rc = opt_in_shared_memory((const void*)metric_kernel, smem)) return rc;
     const float scale = 1.0f / sqrtf((float)HD);
-    metric_kernel<<<H, 256, smem, st>>>(gram_parts, (__nv_bfloat16*)metric, gram, nsplit, scale * scale / (float)L);
+    gram_reduce_kernel<<<dim3(H, HD * HD / 1024), 256, 0, st>>>(gram_parts, nsplit, scale * scale / (float)L);
+    ES_CHECK_LAUNCH("gram_reduce");
+    metric_kernel<<<H, 256, smem, st>>>(gram_parts, (__nv_bfloat16*)metric, gram, nsplit);
     ES_CHECK_LAUNCH("metric");
     probe_kernel<<<dim3(NP, H), HD, 0, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)probes, L, H, nb, scale);
     ES_CHECK_LAUNCH("probes");
@@ -587,10 +659,14 @@ extern "C" int es_reps_kmeans(const void* k, const void* v, const void* metric, 
     if ((k_mean == nullptr) != (v_mean == nullptr)) return set_error(-1, "es_reps_kmeans: give both means or neither");
     const int nb = (L + 63) / 64;
     if (int rc = opt_in_shared_memory((const void*)kmeans_kernel, KM_SMEM)) return rc;
-    kmeans_kernel<<<dim3((nb + KM_BLOCKS - 1) / KM_BLOCKS, H), 256, KM_SMEM, (cudaStream_t)stream>>>(
+    // kv blocks per CTA: KM_BLOCKS share one load of the head's metric; fewer when that would leave the GPU with only a
+    // few waves of CTAs (a handful of heads per GPU), where the last, partly filled wave costs more than the reloads
+    int per = KM_BLOCKS;
+    while (per > 1 && (long long)((nb + per - 1) / per) * H < 8LL * 2 * 148) per >>= 1;
+    kmeans_kernel<<<dim3((nb + per - 1) / per, H), 256, KM_SMEM, (cudaStream_t)stream>>>(
         (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, (const __nv_bfloat16*)metric, (const __nv_bfloat16*)probes,
         (__nv_bfloat16*)k_rep, (__nv_bfloat16*)v_rep, log_counts, (__nv_bfloat16*)k_mean, (__nv_bfloat16*)v_mean, L, H,
-        (nb + 1) * 4, iters);
+        (nb + 1) * 4, iters, per);
     ES_CHECK_LAUNCH("kmeans");
     return 0;
 }
@@ -639,7 +715,9 @@ extern "C" int es_reps_metric_static(const void* q, float* gram, void* metric, v
     const int smem = (2 * HD * 129 + HD) * (int)sizeof(float);
     if (int rc = opt_in_shared_memory((const void*)metric_kernel, smem)) return rc;
     const float scale = 1.0f / sqrtf((float)HD);
-    metric_kernel<<<H, 256, smem, st>>>(parts, (__nv_bfloat16*)metric, gram, nsplit, scale * scale / (float)L);
+    gram_reduce_kernel<<<dim3(H, HD * HD / 1024), 256, 0, st>>>(parts, nsplit, scale * scale / (float)L);
+    ES_CHECK_LAUNCH("gram_reduce");
+    metric_kernel<<<H, 256, smem, st>>>(parts, (__nv_bfloat16*)metric, gram, nsplit);
     ES_CHECK_LAUNCH("metric");
     probe_kernel<<<dim3(NP, H), HD, 0, st>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)probes, L, H, nb, scale);
     ES_CHECK_LAUNCH("probes");
