@@ -13,7 +13,8 @@ attributes `.backend`, `.K`, `._states`, `._buffers`, `._plan_scratch`, `._budge
   the estimate kernel those of all others, so the map needs no clearing between steps.
 * One schedule for every state mode, as a small table of phases:
 
-      DENSE    online-softmax attention over every block; its log2 LSE becomes the branch's offset
+      DENSE    attention over every block: online softmax for the first step of a video, afterwards the previous step's LSE
+               as a fixed offset (flagged tiles recomputed); the log2 LSE becomes the branch's offset
       FULL     every block at the fixed offset: exact output, first map, scales; branch 0 plans the next step
       SPARSE   plan -> lists, block means, representatives, fused step, recomputation + compensation of flagged tiles;
                branch 0 also estimates the skipped masses and plans the next step; later branches reuse branch 0's plan
@@ -117,6 +118,7 @@ class _Branch:
         self.buffers = [torch.full((cdiv(L, BM) * BM, H), 1e30, device=device) for _ in range(2)]
         self.cur = 0
         self.ready = False           # has run the FULL step of this video
+        self.seeded = False          # `offset` holds the LSE of an earlier step of this video
 
     @property
     def offset(self):
@@ -319,7 +321,7 @@ class EchoSparseAttention:
         kernels' status word is read (one device synchronisation per video)."""
         for rec in self._states.values():
             for br in rec.branches.values():
-                br.ready = False
+                br.ready = br.seeded = False
             rec.current = rec.pending = None
         self.check_status()
 
@@ -405,7 +407,17 @@ class EchoSparseAttention:
         phase = self._phase(rec, br, step, branch)
         out = torch.empty_like(q)
         if phase is Phase.DENSE:
-            _dense_into(K, q, k, v, buf, out, br.offset)
+            if br.seeded:
+                # a dense step that follows another step of the same video: its LSE as a fixed offset over every block
+                # (one sweep of QK^T instead of the two of the online-softmax kernel), tiles that leave the safe range
+                # recomputed; exact attention either way
+                K.block_attention(q, k, v, out, buf.all_counts, buf.all_blocks, br.offset, br.next_offset, buf.flags,
+                                  mass=None, threshold=self.threshold)
+                K.exact_fallback(q, k, v, out, buf.all_counts, buf.all_blocks, br.next_offset, buf.flags)
+                br.cur ^= 1
+            else:
+                _dense_into(K, q, k, v, buf, out, br.offset)
+                br.seeded = True
             return out
         top, refined = self._budget(cdiv(L, BK))
         ps = self._sparse_scratch(L, H, q.device, cdiv(refined, 32) * 32)
@@ -441,6 +453,7 @@ class EchoSparseAttention:
         if branch == 0:
             self._plan_next(rec, ps, kept, buf.flags, top, refined, L, sink, step)
         br.cur ^= 1
+        br.seeded = True
         return out
 
     def _expand(self, rec, index, exact, skip, ps):

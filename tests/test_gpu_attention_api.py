@@ -75,6 +75,22 @@ def test_dense_attention_and_lse():
     assert (lse[0].t() * R.LOG2E - lse2).abs().max() < 1e-4
 
 
+def test_dense_steps_after_the_first_run_on_the_previous_lse_and_stay_exact():
+    """The first step of a video runs online softmax; the dense steps that follow take the previous step's LSE as a fixed
+    offset over every block. Both are exact attention, and the stored offset is the step's own log2 LSE."""
+    from self_trainable_or_free_attn_b200.attention import EchoSparseAttention
+    inputs = steps(4, seed=7)
+    attn = EchoSparseAttention(density=0.1, dense_steps=5, dense_layers=())
+    for step, (q, k, v) in enumerate(inputs):
+        out = attn(q, k, v, step, 0, layer=1)
+        ref, lse2 = R.dense_attention(q[0], k[0], v[0])
+        assert rel_err(out[0], ref) < 1e-2, step
+        br = attn._states.record(1).branches[0]
+        assert br.seeded and (br.offset[:L] - lse2).abs().max() < 2e-3, step
+    attn.reset()
+    assert not attn._states.record(1).branches[0].seeded
+
+
 def test_full_density_matches_dense():
     inputs = steps(4)
     outs = run(make(density=1.0), inputs)
