@@ -452,6 +452,37 @@ def vsa2_arm(args, rank, world, local, threads):
     delta = (dout.float() * of.float()).sum(-1)
     ms_kv, _ = timed(lambda: ops._bwd_kv(q, k, v, dout, lse, delta, sel.k2q_ptr, sel.k2q_idx, cnt))
     ms_q, _ = timed(lambda: ops._bwd_q(q, k, v, dout, lse, delta, sel.q2k_ptr, sel.q2k_idx, cnt))
+    # the three-tier fine branch (64 tokens / 4 group means / 1 block mean per kv block): tier A = this selection, tier B the
+    # next 20 % of the pairs by the same local score, tier C the rest; forward alone and forward + backward
+    tiers_line = None
+    if world == 1:
+        from self_trainable_or_free_attn_b200.vsa import tiers as T
+        nb = mask.shape[-1]
+        scores = workloads.local_scores(sh["grid"], heads_all)[:, mine]
+        rest = torch.where(mask, torch.full_like(scores, -1.0), scores).reshape(len(mine), nb * nb)
+        n_b = int(round(0.20 * nb * nb))
+        pick = torch.sort(rest, dim=1, descending=True, stable=True).indices[:, :n_b]
+        tier_ab = mask.clone().reshape(len(mine), nb * nb).scatter_(1, pick, True).reshape(mask.shape)
+        tsel = T.selection_from_masks(mask.to(device), tier_ab.to(device))
+        cols = 64.0 * int(mask.sum()) + 4.0 * n_b * len(mine) + 1.0 * int((~tier_ab).sum())
+        t_flop = 4.0 * 64 * 128 * cols
+
+        def tier_fwd():
+            with torch.no_grad():
+                return T.rep_fine_attention(q, k, v, cnt, tsel, mid_reps=4)
+
+        def tier_both():
+            leaves = [x.detach().requires_grad_(True) for x in (q, k, v)]
+            o, _ = T.rep_fine_attention(*leaves, cnt, tsel, mid_reps=4)
+            return torch.autograd.grad(o, leaves, dout)
+        ms_tf, _ = timed(tier_fwd, 3)
+        ms_tfb, _ = timed(tier_both, 3)
+        tiers_line = {"forward_ms": round(ms_tf, 4), "backward_ms": round(ms_tfb - ms_tf, 4),
+                      "columns_per_query_row_mean": cols / (len(mine) * nb),
+                      "forward_tflops": t_flop / ms_tf / 1e9, "backward_tflops": 2.5 * t_flop / (ms_tfb - ms_tf) / 1e9,
+                      "frac_of_burst_peak_forward": t_flop / ms_tf / 1e9 / measured_peaks()["burst"],
+                      "flop_rule": "4*64*D per (query block, column): 64 columns per tier-A block, 4 per tier-B block, 1 per "
+                                   "tier-C block; backward 2.5 x"}
     extra = 0
     while sampler.count() < 3 and extra < 200:
         step(q, k, v, gate, dout)
@@ -514,6 +545,7 @@ def vsa2_arm(args, rank, world, local, threads):
                                          "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
         "kernel_ms": {"fine_forward": round(ms_f, 4), "fine_backward_kv": round(ms_kv, 4), "fine_backward_q": round(ms_q, 4)},
+        "three_tier_fine_branch": tiers_line,
         "roofline": tensor_roofline("fine forward kernel (es_vsa_attn_fwd)", fwd_tf, ms_f, 5, clocks, peaks, traffic=None),
         "roofline_backward": tensor_roofline("fine backward kernels (es_vsa_attn_bwd_kv + es_vsa_attn_bwd_q)", bwd_tf,
                                              ms_kv + ms_q, 5, clocks, peaks, traffic=None),

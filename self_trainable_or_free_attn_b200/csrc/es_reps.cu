@@ -275,16 +275,35 @@ probe_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ pr
 }
 
 // ------------------------------------------------------------------------------------------------ k-means
-// One CTA (8 warps) per (kv block, head). The two contractions (X = K M, probe scores = P K^T) run on the tensor cores
-// (mma.sync m16n8k16, bf16 products with float32 sums, the arithmetic of the reference's tl.dot on bf16 inputs); the
-// Lloyd iterations work on X in shared memory in float32 with all 256 threads busy in every phase.
+// One CTA (8 warps) per (kv block, head), several blocks in turn. Every contraction runs on the tensor cores
+// (mma.sync m16n8k16 with float32 sums): the probe scores and X = K M on bf16 inputs (the arithmetic of the reference's
+// tl.dot on bf16), the Lloyd iterations on float32 values split into two bf16 halves, x = hi + lo with lo = bf16(x - hi),
+// 16 mantissa bits (the reference's tl.dot on float32 inputs runs as TF32 on a GPU, 10 bits; the golden outputs come
+// from exact float32):
+//   distances   X C^T: the warp's X fragments (hi, lo) stay in registers from the X = K M accumulators; the right operand
+//               has the centroids' upper halves in columns 0-3 and their lower halves in columns 4-7, so two MMAs per
+//               k-step give all four cross products and no column is padding;
+//   centroids   (w X)^T (0 / 1 membership): the token weights are folded into Y = w X once per block, so the membership
+//               operand is exact and two products (Y hi, Y lo) suffice; Y is read back by transposing loads;
+//   final means (0 / 1 membership)^T K and V, exact products.
 constexpr int KS = 136;           // bf16 row stride of the K tile: 272 B, so the 8 rows of an ldmatrix hit distinct banks
-constexpr int XS = 132;           // float row stride of X and of the centroids
+constexpr int XB = 136;           // bf16 row stride of the two halves of Y and of the centroids
 constexpr int PS = 65;            // float row stride of the probe scores
 constexpr int MS = 136;           // bf16 row stride of the metric in shared memory
+constexpr int OS = 72;            // bf16 row stride of the (cluster, token) membership matrix
 constexpr int KM_BLOCKS = 4;      // kv blocks per CTA: the metric is loaded into shared memory once for all of them
-constexpr int KM_SMEM = 128 * MS * 2 + 64 * KS * 2 + 64 * XS * 4 + 64 * PS * 4 + 4 * XS * 4 + 4 * 64 * 4 + 64 * 4 + 64 * 4 +
-                        4 * 64 * 4 * 4 + 2 * 4 * 128 * 4;      // + partial dots [4][64][4] and partial centroid sums [2][4][128]
+constexpr int VS = 136;           // bf16 row stride of the V tile (it takes the place of the probe scores)
+constexpr int KM_SMEM = 128 * MS * 2 + 64 * KS * 2 + 2 * 64 * XB * 2 + 64 * VS * 2 + 8 * XB * 2 + 4 * 64 * 4 + 64 * 4 +
+                        64 * 4 + 2 * 64 * 8 * 4 + 8 * OS * 2;
+static_assert(64 * VS * 2 >= 64 * PS * 4, "the V tile and the probe scores share one area");
+
+__device__ __forceinline__ void split_bf16(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h2 = __floats2bfloat162_rn(x, y);
+    const float2 hf = __bfloat1622float2(h2);
+    const __nv_bfloat162 l2 = __floats2bfloat162_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h2);
+    lo = *reinterpret_cast<const uint32_t*>(&l2);
+}
 
 __global__ void __launch_bounds__(256, 2)
 kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
@@ -295,16 +314,16 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     extern __shared__ __align__(16) uint8_t raw[];
     __nv_bfloat16* sM = reinterpret_cast<__nv_bfloat16*>(raw);                     // [128][MS] the head's metric
     __nv_bfloat16* sK = sM + 128 * MS;                                             // [64][KS]
-    float* sX = reinterpret_cast<float*>(raw + 128 * MS * 2 + 64 * KS * 2);         // [64][XS]
-    float* sP = sX + 64 * XS;                                                       // [64 probes][PS]
-    float* cen = sP + 64 * PS;                                                      // [4][XS]
-    float* wpart = cen + 4 * XS;                                                    // [4][64]
-    float* w = wpart + 4 * 64;                                                      // [64]
-    int* lab = reinterpret_cast<int*>(w + 64);                                      // [64]
-    float* dpart = reinterpret_cast<float*>(lab + 64);                              // [4 d quarters][64 tokens][4 clusters]
-    // dpart is followed by 4 KB more, so that the two together hold [4][4][128] partial sums
-    __shared__ float cw[4], nnp[8];
-    float4* ohw = reinterpret_cast<float4*>(wpart);    // [64 tokens]: the token's weight in the slot of its cluster (wpart is dead by then)
+    __nv_bfloat16* sYh = sK + 64 * KS;                                             // [64][XB] Y = w X, upper halves
+    __nv_bfloat16* sYl = sYh + 64 * XB;                                            // [64][XB] Y, lower halves
+    float* sP = reinterpret_cast<float*>(sYl + 64 * XB);                           // [64 probes][PS]
+    __nv_bfloat16* cen = reinterpret_cast<__nv_bfloat16*>(sP) + 64 * VS;           // [8][XB] centroids: rows 0-3 upper, 4-7 lower halves
+    float* wpart = reinterpret_cast<float*>(cen + 8 * XB);                         // [4][64]
+    float* w = wpart + 4 * 64;                                                     // [64]
+    int* lab = reinterpret_cast<int*>(w + 64);                                     // [64]
+    float* dpart = reinterpret_cast<float*>(lab + 64);                             // [2 d halves][64 tokens][8 columns]
+    __nv_bfloat16* oh = reinterpret_cast<__nv_bfloat16*>(dpart + 2 * 64 * 8);      // [8][OS] (cluster, token) membership, rows 4-7 zero
+    __shared__ float cw[4], cwp[4][4], nnp[8][4];
     __shared__ float s_cnt[4];
     const int h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, tg = lane & 3;
@@ -316,19 +335,11 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
                          metric + ((size_t)h * HD + r) * HD + c16 * 8, 16);
     }
     cp_async_commit();
+    // rows 4-7 of the membership matrix pad the four clusters to the 8 columns of an MMA: zero for good
+    for (int e = tid; e < 8 * OS / 2; e += 256) reinterpret_cast<uint32_t*>(oh)[e] = 0u;
     const int mt = warp & 3, nh = warp >> 2;
-    // this thread's A fragments of the probe scores (probes 16 mt .. +15), the same for every block of the head
-    uint32_t pa[8][4];
-    {
-        const __nv_bfloat16* p0 = probes + ((size_t)h * NP + 16 * mt + g) * HD + 2 * tg;
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks) {
-            pa[ks][0] = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16));
-            pa[ks][1] = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16));
-            pa[ks][2] = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 8));
-            pa[ks][3] = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16 + 8));
-        }
-    }
+    const int lj = lane & 7, lm = lane >> 3;
+    const __nv_bfloat16 one = __float2bfloat16_rn(1.0f), zero = __float2bfloat16_rn(0.0f);
   for (int j = blockIdx.x * blocks_per_cta; j < min(nb, (int)(blockIdx.x + 1) * blocks_per_cta); ++j) {
     const int nvalid = min(L - j * 64, 64);
     __syncthreads();                       // the previous block's readers of the shared tiles are done
@@ -340,43 +351,20 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
                          k + ((size_t)(j * 64 + (okr ? r : 0)) * H + h) * HD + c16 * 8, okr ? 16 : 0);
     }
     cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-
-    // A fragments of this warp's 16 tokens (rows 16 mt ..), all 8 k-steps: shared by both contractions below? No: the
-    // probe scores use K as the B operand. Only X uses these.
+    // this thread's A fragments of the probe scores (probes 16 mt .. +15), requested while the K tile travels
+    uint32_t pa[8][4];
     {
-        // X = K M: rows 16 mt .. +15, columns 64 nh .. +63
-        float acc[8][4];
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt)
-#pragma unroll
-            for (int x = 0; x < 4; ++x) acc[nt][x] = 0.f;
-        const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(sK + (16 * mt + (lane & 15)) * KS + (lane >> 4) * 8);
-        const uint32_t m_addr = (uint32_t)__cvta_generic_to_shared(sM);
-        const int lj = lane & 7, lm = lane >> 3;
+        const __nv_bfloat16* p0 = probes + ((size_t)h * NP + 16 * mt + g) * HD + 2 * tg;
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks) {
-            uint32_t a0, a1, a2, a3;
-            ldmatrix_x4(a_addr + ks * 32, a0, a1, a2, a3);
-#pragma unroll
-            for (int np = 0; np < 4; ++np) {
-                // B[k][n] = M[k][n], row-major in shared memory: transposed 8 x 8 loads, matrices (k lo, n0), (k hi, n0),
-                // (k lo, n0 + 8), (k hi, n0 + 8)
-                const int row = ks * 16 + lj + (lm & 1) * 8, col = 64 * nh + 16 * np + (lm >> 1) * 8;
-                uint32_t b0, b1, b2, b3;
-                ldmatrix_x4_trans(m_addr + (uint32_t)(row * MS + col) * 2, b0, b1, b2, b3);
-                mma16816(acc[2 * np], a0, a1, a2, a3, b0, b1);
-                mma16816(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
-            }
-        }
-#pragma unroll
-        for (int nt = 0; nt < 8; ++nt) {
-            const int col = 64 * nh + 8 * nt + 2 * tg;
-            *reinterpret_cast<float2*>(sX + (16 * mt + g) * XS + col) = make_float2(acc[nt][0], acc[nt][1]);
-            *reinterpret_cast<float2*>(sX + (16 * mt + g + 8) * XS + col) = make_float2(acc[nt][2], acc[nt][3]);
+            pa[ks][0] = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16));
+            pa[ks][1] = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16));
+            pa[ks][2] = __ldg(reinterpret_cast<const uint32_t*>(p0 + ks * 16 + 8));
+            pa[ks][3] = __ldg(reinterpret_cast<const uint32_t*>(p0 + 8 * HD + ks * 16 + 8));
         }
     }
+    cp_async_wait<0>();
+    __syncthreads();
     {
         // probe scores: probes 16 mt .. +15 (A, in registers), tokens 32 nh .. +31 (B = K rows, from shared memory)
         float acc[4][4];
@@ -437,119 +425,193 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
     __syncthreads();
     if (tid < 64) {
         const float sacc = (wpart[tid] + wpart[64 + tid]) + (wpart[128 + tid] + wpart[192 + tid]);
-        const float wt = tid < nvalid ? sacc * ((float)nvalid / (float)NP) : 0.f;
-        w[tid] = wt;
-        lab[tid] = tid >> 4;
-        asm volatile("bar.sync 1, 64;" ::: "memory");          // warps 0 and 1 have read the partial sums that ohw overlays
-        ohw[tid] = make_float4(tid < 16 ? wt : 0.f, (tid >> 4) == 1 ? wt : 0.f, (tid >> 4) == 2 ? wt : 0.f, tid >= 48 ? wt : 0.f);
+        w[tid] = tid < nvalid ? sacc * ((float)nvalid / (float)NP) : 0.f;
     }
+    __syncthreads();
+    // Warp mt of the first four owns tokens 16 mt .. +15: lane (g, tg) keeps the labels of tokens g and g + 8 and writes
+    // cluster tg's column of their rows of the membership matrix; the cluster weights of the 16 tokens are added over the
+    // lanes in a fixed order.
+    const float w_a = w[16 * mt + g], w_b = w[16 * mt + g + 8];
+    int lab_a = mt, lab_b = mt;                       // the initial clusters are the four token quarters
+    auto publish = [&]() {
+        oh[tg * OS + 16 * mt + g] = lab_a == tg ? one : zero;
+        oh[tg * OS + 16 * mt + g + 8] = lab_b == tg ? one : zero;
+        if (tg == 0) { lab[16 * mt + g] = lab_a; lab[16 * mt + g + 8] = lab_b; }
+        float ws = (lab_a == tg ? w_a : 0.f) + (lab_b == tg ? w_b : 0.f);
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+        if (g == 0) cwp[mt][tg] = ws;
+    };
+    if (nh == 0) publish();
     // The probe scores are dead now: their area receives the V tile (64 x 128 bf16), copied asynchronously while the
     // Lloyd iterations run, so the final cluster means do not wait on global memory.
     __nv_bfloat16* sV = reinterpret_cast<__nv_bfloat16*>(sP);
     for (int e = tid; e < 64 * 16; e += 256) {
         const int r = e >> 4, c16 = e & 15;
         const bool okr = r < nvalid;
-        cp_async16_zfill((uint32_t)__cvta_generic_to_shared(sV + r * HD + c16 * 8),
+        cp_async16_zfill((uint32_t)__cvta_generic_to_shared(sV + r * VS + c16 * 8),
                          v + ((size_t)(j * 64 + (okr ? r : 0)) * H + h) * HD + c16 * 8, okr ? 16 : 0);
     }
     cp_async_commit();
+
+    // X = K M: rows 16 mt .. +15, columns 64 nh .. +63. The accumulators of column tiles 2 ks, 2 ks + 1 are, split in two
+    // bf16 halves, this warp's A fragment of k-step ks of the distance products (rows = tokens, k = these 64 dims); the
+    // rows times their tokens' weights go to shared memory for the centroid sums.
+    uint32_t xa_h[4][4], xa_l[4][4];
+    {
+        float acc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[nt][x] = 0.f;
+        const uint32_t a_addr = (uint32_t)__cvta_generic_to_shared(sK + (16 * mt + (lane & 15)) * KS + (lane >> 4) * 8);
+        const uint32_t m_addr = (uint32_t)__cvta_generic_to_shared(sM);
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks) {
+            uint32_t a0, a1, a2, a3;
+            ldmatrix_x4(a_addr + ks * 32, a0, a1, a2, a3);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                // B[k][n] = M[k][n], row-major in shared memory: transposed 8 x 8 loads, matrices (k lo, n0), (k hi, n0),
+                // (k lo, n0 + 8), (k hi, n0 + 8)
+                const int row = ks * 16 + lj + (lm & 1) * 8, col = 64 * nh + 16 * np + (lm >> 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(m_addr + (uint32_t)(row * MS + col) * 2, b0, b1, b2, b3);
+                mma16816(acc[2 * np], a0, a1, a2, a3, b0, b1);
+                mma16816(acc[2 * np + 1], a0, a1, a2, a3, b2, b3);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            uint32_t h0, l0, h1, l1;
+            split_bf16(acc[nt][0], acc[nt][1], h0, l0);        // row g
+            split_bf16(acc[nt][2], acc[nt][3], h1, l1);        // row g + 8
+            xa_h[nt >> 1][(nt & 1) * 2] = h0; xa_h[nt >> 1][(nt & 1) * 2 + 1] = h1;
+            xa_l[nt >> 1][(nt & 1) * 2] = l0; xa_l[nt >> 1][(nt & 1) * 2 + 1] = l1;
+            split_bf16(acc[nt][0] * w_a, acc[nt][1] * w_a, h0, l0);
+            split_bf16(acc[nt][2] * w_b, acc[nt][3] * w_b, h1, l1);
+            const int col = 64 * nh + 8 * nt + 2 * tg;
+            *reinterpret_cast<uint32_t*>(sYh + (16 * mt + g) * XB + col) = h0;
+            *reinterpret_cast<uint32_t*>(sYh + (16 * mt + g + 8) * XB + col) = h1;
+            *reinterpret_cast<uint32_t*>(sYl + (16 * mt + g) * XB + col) = l0;
+            *reinterpret_cast<uint32_t*>(sYl + (16 * mt + g + 8) * XB + col) = l1;
+        }
+    }
     __syncthreads();
 
-    // Weighted centroids of the current labels; keep_old: an emptied cluster keeps its centroid. Also the cluster weights
-    // and the squared norms of the centroids (two warp partials per cluster in nnp).
-    // Thread (token quarter, dim pair) sweeps 16 tokens with the one-hot weights (no branch on the label, every load
-    // independent of the arithmetic); thread (cluster, dim pair) then adds the four quarters in a fixed order. The three
-    // warp reductions of the second phase (cluster weight, squared norm of the new and of the kept centroid) run side by side.
-    float* qpart = dpart;                             // [4 token quarters][4 clusters][128]: dpart and cpart, both dead here
+    // Weighted centroids of the current labels, transposed: rows = this warp's 16 dims, columns = clusters. The warp's
+    // fragments of Y^T (all 64 tokens, both halves) are fetched once per block by transposing loads: matrices (tokens lo,
+    // dims lo), (tokens lo, dims hi), (tokens hi, dims lo), (tokens hi, dims hi). keep_old: an emptied cluster keeps its
+    // centroid (and its squared norm).
+    uint32_t ya_h[4][4], ya_l[4][4];
+#pragma unroll
+    for (int ks = 0; ks < 4; ++ks) {
+        const uint32_t off = (uint32_t)((16 * ks + lj + (lm >> 1) * 8) * XB + 16 * warp + (lm & 1) * 8) * 2;
+        ldmatrix_x4_trans((uint32_t)__cvta_generic_to_shared(sYh) + off, ya_h[ks][0], ya_h[ks][1], ya_h[ks][2], ya_h[ks][3]);
+        ldmatrix_x4_trans((uint32_t)__cvta_generic_to_shared(sYl) + off, ya_l[ks][0], ya_l[ks][1], ya_l[ks][2], ya_l[ks][3]);
+    }
     auto update_centroids = [&](bool keep_old) {
-        {
-            const int dp = 2 * (tid & 63), tq = tid >> 6;
-            float2 sc[4];
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int c = 0; c < 4; ++c) sc[c] = make_float2(0.f, 0.f);
-            // tokens past the valid ones have weight zero
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const int t = 16 * tq + i;
-                const float4 o = ohw[t];
-                const float2 x = *reinterpret_cast<const float2*>(sX + t * XS + dp);
-                sc[0].x = fmaf(o.x, x.x, sc[0].x); sc[0].y = fmaf(o.x, x.y, sc[0].y);
-                sc[1].x = fmaf(o.y, x.x, sc[1].x); sc[1].y = fmaf(o.y, x.y, sc[1].y);
-                sc[2].x = fmaf(o.z, x.x, sc[2].x); sc[2].y = fmaf(o.z, x.y, sc[2].y);
-                sc[3].x = fmaf(o.w, x.x, sc[3].x); sc[3].y = fmaf(o.w, x.y, sc[3].y);
-            }
-#pragma unroll
-            for (int c = 0; c < 4; ++c) *reinterpret_cast<float2*>(qpart + (tq * 4 + c) * 128 + dp) = sc[c];
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(oh + g * OS + 16 * ks + 2 * tg);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(oh + g * OS + 16 * ks + 8 + 2 * tg);
+            mma16816(acc, ya_h[ks][0], ya_h[ks][1], ya_h[ks][2], ya_h[ks][3], b0, b1);
+            mma16816(acc, ya_l[ks][0], ya_l[ks][1], ya_l[ks][2], ya_l[ks][3], b0, b1);
         }
-        __syncthreads();
-        const int c = tid >> 6, d = 2 * (tid & 63);
-        // weight of cluster c: every warp of the cluster adds the 64 tokens in the same order
-        float ws = reinterpret_cast<const float*>(ohw)[4 * lane + c] + reinterpret_cast<const float*>(ohw)[4 * (lane + 32) + c];
-        const float2 p0 = *reinterpret_cast<const float2*>(qpart + (0 * 4 + c) * 128 + d);
-        const float2 p1 = *reinterpret_cast<const float2*>(qpart + (1 * 4 + c) * 128 + d);
-        const float2 p2 = *reinterpret_cast<const float2*>(qpart + (2 * 4 + c) * 128 + d);
-        const float2 p3 = *reinterpret_cast<const float2*>(qpart + (3 * 4 + c) * 128 + d);
-        const float2 old = *reinterpret_cast<const float2*>(cen + c * XS + d);
-        const float s0 = (p0.x + p1.x) + (p2.x + p3.x), s1 = (p0.y + p1.y) + (p2.y + p3.y);
-        float nn_new = s0 * s0 + s1 * s1, nn_old = old.x * old.x + old.y * old.y;
+        // lanes with tg < 2: dims 16 warp + g and + 8 of clusters 2 tg and 2 tg + 1
+        const int ca = (2 * tg) & 3, cb = ca + 1;
+        const float wa = (cwp[0][ca] + cwp[1][ca]) + (cwp[2][ca] + cwp[3][ca]);
+        const float wb = (cwp[0][cb] + cwp[1][cb]) + (cwp[2][cb] + cwp[3][cb]);
+        const bool wr_a = tg < 2 && (!keep_old || wa > 0.f), wr_b = tg < 2 && (!keep_old || wb > 0.f);
+        const float ia = 1.0f / fmaxf(wa, 1e-6f), ib = 1.0f / fmaxf(wb, 1e-6f);
+        uint32_t ha, la, hb, lb;
+        split_bf16(acc[0] * ia, acc[2] * ia, ha, la);          // cluster a: dims g, g + 8
+        split_bf16(acc[1] * ib, acc[3] * ib, hb, lb);          // cluster b
+        const int d = 16 * warp + g;
+        float na = 0.f, nb2 = 0.f;
+        if (wr_a) {
+            cen[ca * XB + d] = __ushort_as_bfloat16((unsigned short)(ha & 0xFFFFu));
+            cen[ca * XB + d + 8] = __ushort_as_bfloat16((unsigned short)(ha >> 16));
+            cen[(4 + ca) * XB + d] = __ushort_as_bfloat16((unsigned short)(la & 0xFFFFu));
+            cen[(4 + ca) * XB + d + 8] = __ushort_as_bfloat16((unsigned short)(la >> 16));
+            const float c0 = bf_lo(ha) + bf_lo(la), c1 = bf_hi(ha) + bf_hi(la);
+            na = c0 * c0 + c1 * c1;
+        }
+        if (wr_b) {
+            cen[cb * XB + d] = __ushort_as_bfloat16((unsigned short)(hb & 0xFFFFu));
+            cen[cb * XB + d + 8] = __ushort_as_bfloat16((unsigned short)(hb >> 16));
+            cen[(4 + cb) * XB + d] = __ushort_as_bfloat16((unsigned short)(lb & 0xFFFFu));
+            cen[(4 + cb) * XB + d + 8] = __ushort_as_bfloat16((unsigned short)(lb >> 16));
+            const float c0 = bf_lo(hb) + bf_lo(lb), c1 = bf_hi(hb) + bf_hi(lb);
+            nb2 = c0 * c0 + c1 * c1;
+        }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            ws += __shfl_xor_sync(0xffffffffu, ws, o);
-            nn_new += __shfl_xor_sync(0xffffffffu, nn_new, o);
-            nn_old += __shfl_xor_sync(0xffffffffu, nn_old, o);
+        for (int o = 4; o < 32; o <<= 1) {
+            na += __shfl_xor_sync(0xffffffffu, na, o);
+            nb2 += __shfl_xor_sync(0xffffffffu, nb2, o);
         }
-        float nn;
-        if (!keep_old || ws > 0.f) {
-            const float inv = 1.0f / fmaxf(ws, 1e-6f);
-            *reinterpret_cast<float2*>(cen + c * XS + d) = make_float2(s0 * inv, s1 * inv);
-            nn = nn_new * (inv * inv);
-        } else {
-            nn = nn_old;
+        if (g == 0) {                                  // the squared norms' shares of these 16 dims
+            if (wr_a) nnp[warp][ca] = na;
+            if (wr_b) nnp[warp][cb] = nb2;
         }
-        if (lane == 0) nnp[warp] = nn;                // warps 2c, 2c + 1 hold cluster c
-        if ((tid & 63) == 0) cw[c] = ws;
+        if (warp == 0 && g == 0 && tg < 2) { cw[ca] = wa; cw[cb] = wb; }
         __syncthreads();
     };
     update_centroids(false);
     for (int it = 0; it < iters; ++it) {
-        // partial dot products: warp -> (d quarter warp % 4, token half warp / 4), lane -> token; the centroid rows are
-        // read as broadcasts, X once; then one thread per token adds the four quarters in a fixed order
+        // the warp's 16 tokens against the four centroids over its 64 dims: columns 0-3 x . c_hi, columns 4-7 x . c_lo
         {
-            const int dq = warp & 3, tk = 32 * (warp >> 2) + lane;
-            float dt[4] = {0.f, 0.f, 0.f, 0.f};
-            const float* xr = sX + tk * XS + 32 * dq;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float4 x = *reinterpret_cast<const float4*>(xr + 4 * i);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float4 y = *reinterpret_cast<const float4*>(cen + c * XS + 32 * dq + 4 * i);
-                    dt[c] = fmaf(x.x, y.x, dt[c]); dt[c] = fmaf(x.y, y.y, dt[c]);
-                    dt[c] = fmaf(x.z, y.z, dt[c]); dt[c] = fmaf(x.w, y.w, dt[c]);
-                }
+            for (int ks = 0; ks < 4; ++ks) {
+                const int d = 64 * nh + 16 * ks + 2 * tg;
+                const uint32_t b0 = *reinterpret_cast<const uint32_t*>(cen + g * XB + d);
+                const uint32_t b1 = *reinterpret_cast<const uint32_t*>(cen + g * XB + d + 8);
+                mma16816(acc, xa_h[ks][0], xa_h[ks][1], xa_h[ks][2], xa_h[ks][3], b0, b1);
+                mma16816(acc, xa_l[ks][0], xa_l[ks][1], xa_l[ks][2], xa_l[ks][3], b0, b1);
             }
-            *reinterpret_cast<float4*>(dpart + (dq * 64 + tk) * 4) = make_float4(dt[0], dt[1], dt[2], dt[3]);
+            float* mine = dpart + (nh * 64 + 16 * mt + g) * 8 + 2 * tg;
+            *reinterpret_cast<float2*>(mine) = make_float2(acc[0], acc[1]);
+            *reinterpret_cast<float2*>(mine + 64) = make_float2(acc[2], acc[3]);
         }
         __syncthreads();
         int differs = 0;
-        if (tid < 64) {                               // one token each
-            const float4 d0 = *reinterpret_cast<const float4*>(dpart + (0 * 64 + tid) * 4);
-            const float4 d1 = *reinterpret_cast<const float4*>(dpart + (1 * 64 + tid) * 4);
-            const float4 d2 = *reinterpret_cast<const float4*>(dpart + (2 * 64 + tid) * 4);
-            const float4 d3 = *reinterpret_cast<const float4*>(dpart + (3 * 64 + tid) * 4);
-            const float dot[4] = {(d0.x + d1.x) + (d2.x + d3.x), (d0.y + d1.y) + (d2.y + d3.y),
-                                  (d0.z + d1.z) + (d2.z + d3.z), (d0.w + d1.w) + (d2.w + d3.w)};
-            float bd = INFINITY;
-            int best = 0;
+        if (nh == 0) {
+            // this warp's 16 tokens: both d halves, then upper + lower centroid halves (lanes tg and tg ^ 2), then the
+            // smaller distance of the lane's two clusters against that of lane tg ^ 1 (ties to the smaller cluster)
+            const float* p0 = dpart + (16 * mt + g) * 8 + 2 * tg;
+            const float2 a0 = *reinterpret_cast<const float2*>(p0), a1 = *reinterpret_cast<const float2*>(p0 + 64 * 8);
+            const float2 b0 = *reinterpret_cast<const float2*>(p0 + 64), b1 = *reinterpret_cast<const float2*>(p0 + 64 * 8 + 64);
+            float da[2] = {a0.x + a1.x, a0.y + a1.y}, db[2] = {b0.x + b1.x, b0.y + b1.y};
 #pragma unroll
-            for (int cc = 0; cc < 4; ++cc) {
-                const float dist = cw[cc] > 0.f ? (nnp[2 * cc] + nnp[2 * cc + 1]) - 2.0f * dot[cc] : INFINITY;
-                if (cc == 0 || dist < bd) { bd = dist; best = cc; }
+            for (int e = 0; e < 2; ++e) {
+                da[e] += __shfl_xor_sync(0xffffffffu, da[e], 2);
+                db[e] += __shfl_xor_sync(0xffffffffu, db[e], 2);
             }
-            differs = tid < nvalid && best != lab[tid];
-            lab[tid] = best;                          // no other thread reads the labels or the one-hot weights in this phase
-            const float wt = w[tid];
-            ohw[tid] = make_float4(best == 0 ? wt : 0.f, best == 1 ? wt : 0.f, best == 2 ? wt : 0.f, best == 3 ? wt : 0.f);
+            const int c0 = (2 * tg) & 3;              // lanes tg and tg ^ 2 hold clusters c0, c0 + 1
+            float dist_a[2], dist_b[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int cc = c0 + e;
+                const float nn = ((nnp[0][cc] + nnp[1][cc]) + (nnp[2][cc] + nnp[3][cc])) +
+                                 ((nnp[4][cc] + nnp[5][cc]) + (nnp[6][cc] + nnp[7][cc]));
+                const bool live = cw[cc] > 0.f;
+                dist_a[e] = live ? nn - 2.0f * da[e] : INFINITY;
+                dist_b[e] = live ? nn - 2.0f * db[e] : INFINITY;
+            }
+            auto pick = [&](const float (&d)[2]) -> int {
+                float bd = d[0];
+                int bi = c0;
+                if (d[1] < bd) { bd = d[1]; bi = c0 + 1; }
+                const float od = __shfl_xor_sync(0xffffffffu, bd, 1);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, 1);
+                return (od < bd || (od == bd && oi < bi)) ? oi : bi;
+            };
+            const int na = pick(dist_a), nb_ = pick(dist_b);
+            differs = (16 * mt + g < nvalid && na != lab_a) || (16 * mt + g + 8 < nvalid && nb_ != lab_b);
+            lab_a = na; lab_b = nb_;
+            publish();
         }
         const int changed = __syncthreads_or(differs);
         update_centroids(true);
@@ -566,45 +628,47 @@ kmeans_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restri
                 s_cnt[c] = (float)n;
                 c4[(size_t)h * nb4 + j * 4 + c] = n > 0 ? log2f((float)n) : -INFINITY;
             }
+            // membership of the valid tokens only (the last readers passed the barrier that ended the iterations)
+            oh[c * OS + lane] = l0 == c ? one : zero;
+            oh[c * OS + lane + 32] = l1 == c ? one : zero;
         }
-        // membership as 0 / 1 in place of the weights (their last readers passed the barrier that ended the iterations)
-        ohw[lane] = make_float4(l0 == 0 ? 1.f : 0.f, l0 == 1 ? 1.f : 0.f, l0 == 2 ? 1.f : 0.f, l0 == 3 ? 1.f : 0.f);
-        ohw[lane + 32] = make_float4(l1 == 0 ? 1.f : 0.f, l1 == 1 ? 1.f : 0.f, l1 == 2 ? 1.f : 0.f, l1 == 3 ? 1.f : 0.f);
     }
     cp_async_wait<0>();
     __syncthreads();
-    {
-        // thread (K or V, token half, dim pair): 32 tokens; a multiply-add with the 0 / 1 membership is an exact add
-        const int which = tid >> 7, th = (tid >> 6) & 1, dp = 2 * (tid & 63);
-        float2 sc[4];
 #pragma unroll
-        for (int c = 0; c < 4; ++c) sc[c] = make_float2(0.f, 0.f);
-        const __nv_bfloat16* src = which ? sV + dp : sK + dp;
-        const int stride = which ? HD : KS;
-#pragma unroll 8
-        for (int i = 0; i < 32; ++i) {
-            const int t = 32 * th + i;
-            const float4 o = ohw[t];
-            const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + t * stride));
-            sc[0].x = fmaf(o.x, x.x, sc[0].x); sc[0].y = fmaf(o.x, x.y, sc[0].y);
-            sc[1].x = fmaf(o.y, x.x, sc[1].x); sc[1].y = fmaf(o.y, x.y, sc[1].y);
-            sc[2].x = fmaf(o.z, x.x, sc[2].x); sc[2].y = fmaf(o.z, x.y, sc[2].y);
-            sc[3].x = fmaf(o.w, x.x, sc[3].x); sc[3].y = fmaf(o.w, x.y, sc[3].y);
+    for (int which = 0; which < 2; ++which) {
+        // (membership)^T K and (membership)^T V: rows = clusters (4 of 16), columns = this warp's 16 dims; products with
+        // 0 / 1 are exact, the sums are float32
+        float acc[2][4];
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) acc[jj][x] = 0.f;
+        const uint32_t src = (uint32_t)__cvta_generic_to_shared(which ? sV : sK);
+        const int stride = which ? VS : KS;
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+            const uint32_t a0 = *reinterpret_cast<const uint32_t*>(oh + g * OS + 16 * ks + 2 * tg);
+            const uint32_t a2 = *reinterpret_cast<const uint32_t*>(oh + g * OS + 16 * ks + 8 + 2 * tg);
+            uint32_t b0, b1, b2, b3;
+            ldmatrix_x4_trans(src + (uint32_t)((16 * ks + lj + (lm & 1) * 8) * stride + 16 * warp + (lm >> 1) * 8) * 2, b0, b1, b2, b3);
+            mma16816(acc[0], a0, 0u, a2, 0u, b0, b1);
+            mma16816(acc[1], a0, 0u, a2, 0u, b2, b3);
         }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) *reinterpret_cast<float2*>(qpart + ((which * 2 + th) * 4 + c) * 128 + dp) = sc[c];
-    }
-    __syncthreads();
-    {
-        const int which = tid >> 7, d = tid & 127;
-        float sacc[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) sacc[c] = qpart[((which * 2 + 0) * 4 + c) * 128 + d] + qpart[((which * 2 + 1) * 4 + c) * 128 + d];
-        __nv_bfloat16* o = (which ? v4 : k4) + ((size_t)h * nb4 + j * 4) * HD + d;
-#pragma unroll
-        for (int c = 0; c < 4; ++c) o[c * HD] = __float2bfloat16_rn(sacc[c] * (1.0f / fmaxf(s_cnt[c], 1.0f)));
+        const float inv = g < 4 ? 1.0f / fmaxf(s_cnt[g], 1.0f) : 0.f;
+        __nv_bfloat16* o = (which ? v4 : k4) + ((size_t)h * nb4 + j * 4 + (g & 3)) * HD + 16 * warp + 2 * tg;
         __nv_bfloat16* mo = which ? vm : km;
-        if (mo) mo[((size_t)j * H + h) * HD + d] = __float2bfloat16_rn(((sacc[0] + sacc[1]) + (sacc[2] + sacc[3])) / (float)nvalid);
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+            if (g < 4) *reinterpret_cast<__nv_bfloat162*>(o + 8 * jj) = __floats2bfloat162_rn(acc[jj][0] * inv, acc[jj][1] * inv);
+            // block mean: the four clusters' sums, (0 + 1) + (2 + 3), held by lanes 4 c + tg
+            float t0 = acc[jj][0], t1 = acc[jj][1];
+            t0 += __shfl_xor_sync(0xffffffffu, t0, 4); t1 += __shfl_xor_sync(0xffffffffu, t1, 4);
+            t0 += __shfl_xor_sync(0xffffffffu, t0, 8); t1 += __shfl_xor_sync(0xffffffffu, t1, 8);
+            if (mo && g == 0)
+                *reinterpret_cast<__nv_bfloat162*>(mo + ((size_t)j * H + h) * HD + 16 * warp + 8 * jj + 2 * tg) =
+                    __floats2bfloat162_rn(t0 / (float)nvalid, t1 / (float)nvalid);
+        }
     }
   }
 }

@@ -119,6 +119,26 @@ def test_operator_matches_the_sampled_oracle_with_and_without_split_kv(layer, ca
             _check(got, _fine_lse(layer, sel), layer, sel, heads_whole=(), seed=1)
 
 
+@pytest.mark.parametrize("case", ["hot_kv", "straggler"])
+def test_hot_kv_blocks_and_a_straggler_row_under_the_automatic_split(layer, case):
+    """NB / 16 kv blocks that every query block selects (long kv->q lists: the backward's kv pass) and one query block that
+    selects every kv block (one long q->kv list): the automatic split policy against the unsplit kernels and, on sampled
+    blocks of every head (the longest lists among them), against the sampled oracle."""
+    from self_trainable_or_free_attn_b200 import vsa
+    from self_trainable_or_free_attn_b200.vsa import workloads
+    sel, nb = workloads.selection(case, GRID, HEADS, TOPK, DEV)
+    rows = sel.row_counts().reshape(HEADS, NB)
+    assert nb == NB and bool((rows.sum(1) == NB * TOPK).all())
+    if case == "straggler":
+        assert bool((rows[:, NB - 1] == NB).all())
+    base = _run(layer, sel, None)
+    got = _run(layer, sel, vsa.SplitKV.auto())
+    for what, a, b in zip(("o", "dq", "dk", "dv", "dgate"), got, base):
+        err = float((a.float() - b.float()).abs().max())
+        assert err <= 1e-2 * float(b.float().abs().max()), (case, what, err)
+    _check(got, _fine_lse(layer, sel), layer, sel, heads_whole=(), seed=2)
+
+
 def test_three_tier_fine_branch_matches_the_dense_tier_oracle_at_512_blocks(layer):
     """Tier A = the even selection (32 / 512 of the pairs), tier B the next 20 % of the same score, tier C the rest: two
     heads on the GPU, every query block and every kv block of head 1 against the closed-form tier oracle."""
