@@ -710,6 +710,31 @@ def main():
         e1.record()
         barrier()
         ms_e2e = e0.elapsed_time(e1)
+    # the exchanges of a sequence-sharded caller alone: q, k, v in and the output back, both branches, as in one step
+    exchange = None
+    if args.ulysses and dist is not None:
+        from self_trainable_or_free_attn_b200 import ulysses
+        outs = [torch.empty(1, L, len(heads), 128, device=device, dtype=torch.bfloat16) for _ in inputs]
+
+        def exchanges():
+            for (q, k, v), o in zip(inputs, outs):
+                for t in (q[0], k, v):
+                    ulysses.seq_to_heads(t)
+                ulysses.heads_to_seq(o)
+        exchanges()
+        barrier()
+        e0.record()
+        for _ in range(5):
+            exchanges()
+        e1.record()
+        barrier()
+        ms_x = e0.elapsed_time(e1) / 5
+        sent = sum(4 * k.numel() * 2 for _, k, _ in inputs) * (world - 1) // world      # bytes this rank sends to its peers
+        xs = torch.tensor([ms_x], device=device, dtype=torch.float64)
+        dist.all_reduce(xs, op=dist.ReduceOp.MAX)
+        exchange = {"all_to_alls_per_step": 4 * len(inputs), "ms_per_step": float(xs[0]),
+                    "bytes_sent_per_rank_per_step": sent, "gb_per_s_per_rank_per_direction": sent / float(xs[0]) / 1e6,
+                    "how": "the eight all_to_all_single calls of a step and their layout copies, timed alone (max over ranks)"}
     # dense steps of branch 0: the first of a video (online softmax over every block) and one that follows it (the previous
     # step's LSE as a fixed offset over every block, flagged tiles recomputed)
     attn.reset()
@@ -775,6 +800,7 @@ def main():
         "kernel_ms_per_step": {n: round(sum(timer.ms(n)) / args.steps, 3) for n in names if timer.events[n]},
         "dense_step_ms_per_branch": round(ms_dense, 3),
         "dense_first_step_ms_per_branch": round(ms_dense_first, 3),
+        "ulysses_exchange": exchange,
         "roofline": tensor_roofline(
             "attention_kernel<0> (es_sparse_attention)", achieved, k_ms, len(kernel_ms), clocks, peaks, traffic=traffic,
             traffic_source="dram__bytes_read.sum + dram__bytes_write.sum of one launch captured at the Wan-1.3B shape "
