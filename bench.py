@@ -439,15 +439,18 @@ def vsa2_arm(args, rank, world, local, threads):
     launches = _native.launch_count() - launches0
     # the fine kernels alone (CUDA events on the launching stream), same inputs
     def timed(fn, n=5):
+        """Median of n separately timed calls after one untimed call (one stall of the allocator does not move it)."""
         fn()
         torch.cuda.synchronize()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
+        ts = []
         for _ in range(n):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
             out = fn()
-        b.record()
-        torch.cuda.synchronize()
-        return a.elapsed_time(b) / n, out
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        return statistics.median(ts), out
     ms_f, (of, lse) = timed(lambda: ops.attn_fwd(q, k, v, sel.q2k_ptr, sel.q2k_idx, cnt))
     delta = (dout.float() * of.float()).sum(-1)
     ms_kv, _ = timed(lambda: ops._bwd_kv(q, k, v, dout, lse, delta, sel.k2q_ptr, sel.k2q_idx, cnt))
