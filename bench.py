@@ -587,8 +587,10 @@ def main():
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ulysses", action="store_true",
-                    help="N > 1 only: the caller is sequence-sharded; q, k, v and the output cross the ranks by all-to-all "
-                         "(NCCL) inside the timed region, the attention itself stays head-sharded")
+                    help="N > 1 only: the caller is sequence-sharded; q, k, v and the output cross the ranks inside the timed "
+                         "region (this library's exchange kernel over peer memory), the attention itself stays head-sharded")
+    ap.add_argument("--nccl-exchange", action="store_true",
+                    help="--ulysses: run the exchanges as all_to_all_single between two layout copies instead")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -633,7 +635,15 @@ def main():
             raise SystemExit(f"--ulysses needs tokens ({L}) and heads ({heads_all}) divisible by the ranks ({world})")
         inputs = [(tuple(ulysses.heads_to_seq(t) for t in q), ulysses.heads_to_seq(k), ulysses.heads_to_seq(v))
                   for q, k, v in inputs]
-        attn_call = ulysses.UlyssesAttention(attn)
+        attn_call = ulysses.UlyssesAttention(attn, peer_memory=not args.nccl_exchange)
+        if attn_call.peer is not None:
+            # the peer-memory exchange against the all-to-all between two layout copies, both directions, once
+            q0 = inputs[0][1]
+            a, b = attn_call.peer.seq_to_heads(q0, "check_in"), ulysses.seq_to_heads(q0)
+            c, d = attn_call.peer.heads_to_seq(b, "check_out"), ulysses.heads_to_seq(b)
+            torch.cuda.synchronize()
+            if not (torch.equal(a, b) and torch.equal(c, d) and torch.equal(c, q0)):
+                raise SystemExit("the peer-memory exchange differs from all_to_all_single")
     else:
         attn_call = attn
 
@@ -721,9 +731,14 @@ def main():
 
         def exchanges():
             for (q, k, v), o in zip(inputs, outs):
-                for t in (q[0], k, v):
-                    ulysses.seq_to_heads(t)
-                ulysses.heads_to_seq(o)
+                if attn_call.peer is not None:
+                    for t, role in ((q[0], "q"), (k, "k"), (v, "v")):
+                        attn_call.peer.seq_to_heads(t, role)
+                    attn_call.peer.heads_to_seq(o, "out")
+                else:
+                    for t in (q[0], k, v):
+                        ulysses.seq_to_heads(t)
+                    ulysses.heads_to_seq(o)
         exchanges()
         barrier()
         e0.record()
@@ -735,9 +750,11 @@ def main():
         sent = sum(4 * k.numel() * 2 for _, k, _ in inputs) * (world - 1) // world      # bytes this rank sends to its peers
         xs = torch.tensor([ms_x], device=device, dtype=torch.float64)
         dist.all_reduce(xs, op=dist.ReduceOp.MAX)
-        exchange = {"all_to_alls_per_step": 4 * len(inputs), "ms_per_step": float(xs[0]),
+        exchange = {"path": "all_to_all_single between two layout copies (NCCL)" if attn_call.peer is None else
+                            "es_exchange_rows into the peers' receive buffers (peer memory) + a 4-byte all-reduce",
+                    "exchanges_per_step": 4 * len(inputs), "ms_per_step": float(xs[0]),
                     "bytes_sent_per_rank_per_step": sent, "gb_per_s_per_rank_per_direction": sent / float(xs[0]) / 1e6,
-                    "how": "the eight all_to_all_single calls of a step and their layout copies, timed alone (max over ranks)"}
+                    "how": "the exchanges of a step (q, k, v in, the output back, every branch) timed alone, max over ranks"}
     # dense steps of branch 0: the first of a video (online softmax over every block) and one that follows it (the previous
     # step's LSE as a fixed offset over every block, flagged tiles recomputed)
     attn.reset()

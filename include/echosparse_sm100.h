@@ -34,6 +34,18 @@ int es_device_status(int32_t* status_out);
  * afterwards, or the attention kernels of this device stay switched off. */
 int es_selftest_wait_timeout(int32_t limit_us, void* stream);
 
+/* Sequence <-> head exchange of a sequence-sharded caller, one kernel per rank: for every peer p < peers, `rows` rows of
+ * `row_bytes` bytes are read from src + p * src_slab_stride + i * src_row_stride and stored at
+ * dst_ptrs[p] + dst_offset + i * dst_row_stride, where dst_ptrs[p] is rank p's receive buffer as mapped on this GPU (a peer
+ * mapping; this rank's own entry is an ordinary pointer). dst_ptrs is a HOST array of `peers` pointers (1 .. 16). All
+ * pointers, strides, offsets and row_bytes are multiples of 16. The kernel waits on nobody: the caller orders it against the
+ * peers' use of the buffers with a collective on the same stream before the data is read and before a buffer is written
+ * again. Replaces the pair of layout copies and the torch.distributed.all_to_all_single of the reference's sequence-parallel
+ * recipe around its processor (no single reference function; README, multi-GPU section). */
+int es_exchange_rows(const void* src, int64_t src_slab_stride, int64_t src_row_stride, void* const* dst_ptrs,
+                     int64_t dst_offset, int64_t dst_row_stride, int32_t peers, int64_t rows, int32_t row_bytes,
+                     void* stream);
+
 /* Exact attention over a list of 64-token blocks at a fixed softmax offset, with per-block masses.
  * Replaces echosparse/kernels/block_attention.py:327 `block_attention(q, k, v, out, counts, blocks, offset, lse, flags,
  * mass, threshold)`. counts (nq, H) int32; blocks (nq, H, nk) int32 ascending; flags (nq, H) int32 out;

@@ -15,6 +15,7 @@ LIB_PATH = os.environ.get("ECHOSPARSE_SM100_LIB") or os.path.join(_HERE, "_lib",
 _P = ctypes.c_void_p
 _I = ctypes.c_int32
 _F = ctypes.c_float
+_I64 = ctypes.c_int64
 
 # name -> argument types (all return int unless listed in _RESTYPES)
 SIGNATURES = {
@@ -23,6 +24,7 @@ SIGNATURES = {
     "es_launch_count": [],
     "es_device_status": [_P],
     "es_selftest_wait_timeout": [_I, _P],
+    "es_exchange_rows": [_P, _I64, _I64, _P, _I64, _I64, _I, _I64, _I, _P],
     "es_block_attention": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F, _P],
     "es_sparse_attention": [_P, _P, _P, _P, _P, _P, _I, _P, _P, _P, _I, _P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _F,
                             _P],

@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT_DIR = os.path.join(HERE, "_lib")
 LIB = os.path.join(OUT_DIR, "libechosparse_sm100.so")
-SOURCES = ["es_api.cu", "es_attention.cu", "es_select.cu", "es_small.cu", "es_reps.cu", "es_vsa_attn.cu", "es_vsa_misc.cu", "es_vsa_split.cu", "es_vsa_tiers.cu"]
+SOURCES = ["es_api.cu", "es_attention.cu", "es_select.cu", "es_small.cu", "es_reps.cu", "es_exchange.cu", "es_vsa_attn.cu", "es_vsa_misc.cu", "es_vsa_split.cu", "es_vsa_tiers.cu"]
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "-Xcompiler", "-fPIC"]
 
 
