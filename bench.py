@@ -667,8 +667,16 @@ def main():
     ms = e0.elapsed_time(e1)
     launches = _native.launch_count() - launches0
     K.set_kernel_timer(None)
+    def some_rank_wants_more():
+        """The same answer on every rank (the steps of a sequence-sharded caller contain collectives, so every rank must
+        run the same number of them)."""
+        want = torch.tensor([1 if sampler.count() < 3 else 0], device=device, dtype=torch.int32)
+        if dist is not None:
+            dist.all_reduce(want, op=dist.ReduceOp.MAX)
+        return bool(int(want[0]))
+
     extra = 0
-    while sampler.count() < 3 and extra < 40:          # nvidia-smi needs ~0.3 s for its first lines: keep the load on
+    while extra < 40 and some_rank_wants_more():       # nvidia-smi needs ~0.3 s for its first lines: keep the load on
         run_steps(attn_call, inputs, 2 + args.warmup + args.steps + extra, 2, sink)
         torch.cuda.synchronize()
         extra += 2
