@@ -59,6 +59,21 @@ def heads_to_seq(y, group=None):
     return recv.permute(1, 0, 2, 3).reshape(1, L // world, world * Hl, D)
 
 
+def seq_to_heads_plan(rank, world, Ll, H, D, elem):
+    """Arguments of `es_exchange_rows` for rank `rank`'s [Ll, H, D] tokens on the way to heads, in bytes:
+    (src_slab_stride, src_row_stride, dst_offset, dst_row_stride, rows, row_bytes). Peer p takes columns
+    [p Hl D, (p + 1) Hl D) of every row; they become rows [rank Ll, (rank + 1) Ll) of its [world Ll, Hl, D] buffer."""
+    Hl = H // world
+    return Hl * D * elem, H * D * elem, rank * Ll * Hl * D * elem, Hl * D * elem, Ll, Hl * D * elem
+
+
+def heads_to_seq_plan(rank, world, L, Hl, D, elem):
+    """The same for rank `rank`'s [L, Hl, D] heads on the way back: peer p takes rows [p Ll, (p + 1) Ll); they become
+    columns [rank Hl D, (rank + 1) Hl D) of the rows of its [Ll, world Hl, D] buffer."""
+    Ll = L // world
+    return Ll * Hl * D * elem, Hl * D * elem, rank * Hl * D * elem, world * Hl * D * elem, Ll, Hl * D * elem
+
+
 class PeerExchange:
     """The two exchanges through peer memory. One object per process group; receive buffers are made once per (role, shape)
     by a collective call (every rank must ask for the same roles and shapes in the same order) and are handed out as the
@@ -108,10 +123,8 @@ class PeerExchange:
         Ll, H, D = t.shape
         if H % self.world != 0:
             raise ValueError(f"{H} heads cannot be divided over {self.world} ranks")
-        Hl, es = H // self.world, t.element_size()
-        recv, _, ptrs = self._receive_buffer(role, (1, self.world * Ll, Hl, D), t.dtype, t.device)
-        # peer p takes columns [p Hl D, (p + 1) Hl D) of every row; they become rows [r Ll, (r + 1) Ll) of its buffer
-        self._run(t, ptrs, Hl * D * es, H * D * es, self.rank * Ll * Hl * D * es, Hl * D * es, Ll, Hl * D * es)
+        recv, _, ptrs = self._receive_buffer(role, (1, self.world * Ll, H // self.world, D), t.dtype, t.device)
+        self._run(t, ptrs, *seq_to_heads_plan(self.rank, self.world, Ll, H, D, t.element_size()))
         self._landed(t.device)
         return recv
 
@@ -123,10 +136,8 @@ class PeerExchange:
         L, Hl, D = t.shape
         if L % self.world != 0:
             raise ValueError(f"{L} tokens cannot be divided over {self.world} ranks")
-        Ll, es = L // self.world, t.element_size()
-        recv, _, ptrs = self._receive_buffer(role, (1, Ll, self.world * Hl, D), t.dtype, t.device)
-        # peer p takes rows [p Ll, (p + 1) Ll); they become columns [r Hl D, (r + 1) Hl D) of its buffer's rows
-        self._run(t, ptrs, Ll * Hl * D * es, Hl * D * es, self.rank * Hl * D * es, self.world * Hl * D * es, Ll, Hl * D * es)
+        recv, _, ptrs = self._receive_buffer(role, (1, L // self.world, self.world * Hl, D), t.dtype, t.device)
+        self._run(t, ptrs, *heads_to_seq_plan(self.rank, self.world, L, Hl, D, t.element_size()))
         self._landed(t.device)
         return recv
 

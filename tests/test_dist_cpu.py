@@ -109,3 +109,39 @@ def test_ulysses_exchange_round_trip_and_attention_equivalence(tmp_path):
         assert res["ok_fwd"] and res["ok_back"], "exchange is not the head / sequence transposition"
         assert res["err"] < 1e-6, "sequence-sharded attention differs from the unsharded one"
         assert "cannot be divided" in res["bad"]
+
+
+def _emulate_exchange_rows(src, bufs, slab_stride, src_row, dst_offset, dst_row, rows, row_bytes):
+    """What es_exchange_rows does, on host byte arrays: for every peer, `rows` rows of `row_bytes`."""
+    for p, dst in enumerate(bufs):
+        for i in range(rows):
+            a = p * slab_stride + i * src_row
+            b = dst_offset + i * dst_row
+            assert a + row_bytes <= src.size and b + row_bytes <= dst.size, "a row leaves its buffer"
+            dst[b:b + row_bytes] = src[a:a + row_bytes]
+
+
+@pytest.mark.parametrize("P,Ll,Hl", [(2, 6, 3), (4, 5, 2), (8, 3, 3), (8, 4, 1)])
+def test_exchange_plans_address_exactly_the_all_to_all_transposition(P, Ll, Hl):
+    """The byte addressing that PeerExchange hands to the exchange kernel (ulysses.seq_to_heads_plan / heads_to_seq_plan),
+    replayed on the host for every rank: each receive buffer ends up as the head shard (and, on the way back, the token
+    shard) of the unsharded tensor, every byte written exactly once."""
+    import numpy as np
+    from self_trainable_or_free_attn_b200 import ulysses
+    D, es = 8, 2
+    H, L = P * Hl, P * Ll
+    full = np.arange(L * H * D, dtype=np.int16).reshape(L, H, D)
+    seq = [np.ascontiguousarray(full[r * Ll:(r + 1) * Ll]) for r in range(P)]
+    heads = [np.ascontiguousarray(full[:, r * Hl:(r + 1) * Hl]) for r in range(P)]
+    recv = [np.full(L * Hl * D * es, 0xEE, dtype=np.uint8) for _ in range(P)]
+    for r in range(P):
+        _emulate_exchange_rows(seq[r].view(np.uint8).reshape(-1), recv, *ulysses.seq_to_heads_plan(r, P, Ll, H, D, es))
+    for r in range(P):
+        assert np.array_equal(recv[r].view(np.int16).reshape(L, Hl, D), heads[r]), r
+    back = [np.full(Ll * H * D * es, 0xEE, dtype=np.uint8) for _ in range(P)]
+    for r in range(P):
+        _emulate_exchange_rows(heads[r].view(np.uint8).reshape(-1), back, *ulysses.heads_to_seq_plan(r, P, L, Hl, D, es))
+    for r in range(P):
+        assert np.array_equal(back[r].view(np.int16).reshape(Ll, H, D), seq[r]), r
+    for plan in (ulysses.seq_to_heads_plan(P - 1, P, Ll, H, D, es), ulysses.heads_to_seq_plan(P - 1, P, L, Hl, D, es)):
+        assert all(x % 16 == 0 for x in plan[:4]) and plan[5] % 16 == 0      # what the kernel requires of strides and rows

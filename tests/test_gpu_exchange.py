@@ -20,6 +20,7 @@ def _launch(src, bufs, slab_stride, src_row, dst_offset, dst_row, rows, row_byte
 
 @pytest.mark.parametrize("P,Ll,Hl", [(2, 96, 3), (4, 50, 2), (8, 33, 1)])
 def test_both_directions_equal_the_all_to_all_transposition(P, Ll, Hl):
+    from self_trainable_or_free_attn_b200 import ulysses
     D, es = 128, 2
     H, L = P * Hl, P * Ll
     g = torch.Generator(device="cuda").manual_seed(P)
@@ -29,13 +30,13 @@ def test_both_directions_equal_the_all_to_all_transposition(P, Ll, Hl):
     # sequence -> heads
     recv = [torch.full((L, Hl, D), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(P)]
     for r in range(P):
-        _launch(seq[r], recv, Hl * D * es, H * D * es, r * Ll * Hl * D * es, Hl * D * es, Ll, Hl * D * es)
+        _launch(seq[r], recv, *ulysses.seq_to_heads_plan(r, P, Ll, H, D, es))
     for r in range(P):
         assert torch.equal(recv[r], heads[r]), r
     # heads -> sequence
     back = [torch.full((Ll, H, D), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(P)]
     for r in range(P):
-        _launch(heads[r], back, Ll * Hl * D * es, Hl * D * es, r * Hl * D * es, H * D * es, Ll, Hl * D * es)
+        _launch(heads[r], back, *ulysses.heads_to_seq_plan(r, P, L, Hl, D, es))
     for r in range(P):
         assert torch.equal(back[r], seq[r]), r
 
