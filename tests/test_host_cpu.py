@@ -78,3 +78,83 @@ def test_state_table_views():
         attn._states[(2, 3)]
     attn._states.clear()
     assert not attn._states
+
+
+class _RecordingKernels:
+    """A kernel set that only writes down which entry points the processor calls, in order."""
+
+    def __init__(self):
+        self.calls = []
+
+        outer = self
+
+        class Representatives:
+            def __init__(self, L, H, D, device, iters=6):
+                nb = -(-L // 64)
+                self.k = torch.zeros(H, (nb + 1) * 4, D)
+                self.v = torch.zeros(H, (nb + 1) * 4, D)
+                self.log_counts = torch.zeros(H, (nb + 1) * 4)
+
+            def build(self, q, k, v, k_mean=None, v_mean=None):
+                outer.calls.append("reps.build")
+
+        self.Representatives = Representatives
+
+    def __getattr__(self, name):
+        def record(*args, **kwargs):
+            self.calls.append(name if name != "block_attention" or kwargs.get("mass") is None else "block_attention+mass")
+        return record
+
+    def take(self):
+        got, self.calls = self.calls, []
+        return got
+
+
+def test_schedule_of_kernel_calls_over_a_video():
+    """The processor's phases, seen as the sequence of kernel-set calls (no GPU: a recording kernel set on CPU tensors):
+    first dense step = online softmax; later dense steps = fixed offset + recomputation; full step; sparse steps with the
+    plan of branch 0 reused by branch 1, two plans alternating; a skipped step falls back to a dense step; reset() starts
+    over."""
+    L, H = 64 * 6, 1
+    attn = EchoSparseAttention(density=0.25, dense_steps=3, dense_layers=())
+    K = attn.K = _RecordingKernels()
+    q = torch.zeros(L, H, 128, dtype=torch.bfloat16)
+    run = lambda step, branch: (attn._step(q, q, q, step, branch, 7, attention.NO_SINK), K.take())[1]
+    first_dense = ["exact_fallback"]
+    later_dense = ["block_attention", "exact_fallback"]
+    sparse = ["rebuild_plan", "block_means", "reps.build", "sparse_attention", "exact_fallback", "compensate_fallback"]
+    plan = ["select_blocks", "pack_plan"]
+    assert run(0, 0) == first_dense and run(0, 1) == first_dense
+    assert run(1, 0) == later_dense and run(1, 1) == later_dense
+    rec = attn._states.record(7)
+    assert rec.current is None and rec.pending is None and not rec.ready
+    assert run(2, 0) == ["block_attention+mass", "exact_fallback", "full_step_scales"] + plan
+    assert rec.pending == (0, 3) and rec.ready == {0}
+    assert run(2, 1) == later_dense and rec.ready == {0, 1}
+    assert run(3, 0) == sparse + ["estimate_skipped"] + plan
+    assert rec.current == (0, 3) and rec.pending == (1, 4)           # the other plan is written while this one is read
+    assert run(3, 1) == sparse
+    assert run(4, 0) == sparse + ["estimate_skipped"] + plan and rec.current == (1, 4) and rec.pending == (0, 5)
+    # the offsets swap roles every step that writes an LSE
+    br = rec.branches[0]
+    assert br.cur == 0 and br.seeded                 # steps 1, 2, 3, 4 swapped four times
+    # step 5 is skipped: the pending plan was made for step 5, not 6 -> a dense step on the previous LSE
+    assert run(6, 0) == later_dense and rec.current is None and rec.pending is None
+    assert run(6, 1) == later_dense
+    attn.reset()
+    assert not rec.ready and not br.seeded
+    assert run(0, 0) == first_dense
+
+
+def test_layer_state_keeps_its_lists_and_skips_the_rebuild():
+    L, H = 64 * 6, 1
+    attn = EchoSparseAttention(density=0.25, dense_steps=2, dense_layers=(), state="layer")
+    K = attn.K = _RecordingKernels()
+    q = torch.zeros(L, H, 128, dtype=torch.bfloat16)
+    for step in range(2):
+        attn._step(q, q, q, step, 0, 1, attention.NO_SINK)
+    K.take()
+    attn._step(q, q, q, 2, 0, 1, attention.NO_SINK)
+    calls = K.take()
+    assert "rebuild_plan" not in calls and calls[:3] == ["block_means", "reps.build", "sparse_attention"]
+    assert sorted(attn._states.record(1).expanded) == [0, 1]
