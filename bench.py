@@ -150,8 +150,10 @@ def workload_config(args, world=1):
     return {"workload": args.workload, "tokens": synthetic.grid_tokens(grid) + text, "heads": heads, "branches": branches,
             "density": density, "head_dim": 128, "flag_threshold_log2": args.threshold,
             "partition": (f"heads over {world} GPU(s), both CFG branches of a head together"
-                          + ("; sequence-sharded caller: q, k, v and the output cross the ranks by NCCL all-to-all every step "
-                             "(Ulysses)" if args.ulysses and world > 1 else "")),
+                          + ("; sequence-sharded caller (Ulysses): q, k, v and the output cross the ranks every step, by "
+                             + ("all_to_all_single between two layout copies" if getattr(args, "nccl_exchange", False)
+                                else "this library's exchange kernel over peer memory")
+                             if args.ulysses and world > 1 else "")),
             "l2": "inputs (q, k, v of a branch >> 126 MB) exceed L2 between iterations",
             "step": "one sparse-step attention layer, both CFG branches: plan -> lists, block means, representatives, fused "
                     "sparse attention, fallback of flagged tiles, estimates, next plan"}
